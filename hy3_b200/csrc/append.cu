@@ -1,0 +1,284 @@
+/*
+ * append.cu -- fused per-head QK RMSNorm + rotate_half RoPE + KV quantise + append,
+ * plus the cache import/export/fill utilities that share its store path.
+ *
+ * One warp owns one 128-wide head row (4 dims per lane, lanes 0-15 hold dims 0..63 and
+ * lanes 16-31 hold dims 64..127, so the rotate_half partner d+64 is lane^16).  One launch
+ * covers every row of the step's batch: 64 Q heads + 8 K heads + 8 V heads per token,
+ * where the reference launches qk_norm_rope_fused_kernel and kv_quantize_* once per token
+ * (hy3_gpu.cu:823-829).  HBM-bound, a few KB per token: the job of this kernel is to be one
+ * launch, coalesced (512 B per warp load, 128 B per warp code store) and bit-faithful.
+ *
+ * Arithmetic follows the reference CUDA kernels operation for operation:
+ *   - sum of squares in the reference's shared-memory tree order (hy3_gpu.cu:155-157):
+ *     (d, d+64), then (d, d+32), ... reproduced with xor-shuffles 16,8,4,2,1 and the
+ *     last two levels in registers;
+ *   - r = rsqrtf(ss/128 + eps), y = x*r*w (hy3_gpu.cu:158-159);
+ *   - RoPE angle (float)pos*inv_freq[d], full-range cosf/sinf, attn_factor on both
+ *     (hy3_gpu.cu:161-163), position probe (ti + (ti>=jump_at ? jump : 0))*stride (:152);
+ *   - quantiser: s = absmax/127 (or /7) + 1e-8, inv = 1/s, code = roundf(clamp(x*inv)),
+ *     stored scale = fp16(s) (hy3_gpu.cu:260-269, :338-351), IEEE division (no fast-math).
+ */
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "ctx.h"
+
+namespace {
+
+__device__ __forceinline__ uint8_t *page_ptr(const hy3a_cache_view &c, int seq, int slot, int layer, int head_local) {
+    int block = c.block_table[(size_t)seq * c.max_blocks_per_seq + (slot >> 7)];
+    return c.pool + hy3a_page_index(c, block, layer, head_local) * (size_t)c.page_bytes;
+}
+
+/* Quantise (or round to fp16) the warp's 128 values y[4] (dims d0..d0+3 per lane) and
+ * store them as row `tok` (0..127) of the page.  is_v selects the V area / pair layout.
+ * Returns the fp16 scale bits (0 for FP16 caches).                                    */
+template <int DT>
+__device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g, int tok, bool is_v, const float y[4], int d0, int lane) {
+    if (DT == 0) {
+        __half2 h01 = __floats2half2_rn(y[0], y[1]);
+        __half2 h23 = __floats2half2_rn(y[2], y[3]);
+        uint2 w;
+        w.x = *reinterpret_cast<unsigned *>(&h01);
+        w.y = *reinterpret_cast<unsigned *>(&h23);
+        int off = is_v ? g.v_off + hy3a_v16_dim_off(tok, d0) : hy3a_k_dim_off<0>(tok, d0);
+        *reinterpret_cast<uint2 *>(page + off) = w;
+        return 0u;
+    }
+    float m = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float qmax = (DT == 1) ? 127.f : 7.f;
+    float s = __fadd_rn(__fdiv_rn(m, qmax), 1e-8f);
+    float inv = __fdiv_rn(1.f, s);
+    int c[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) c[j] = (int)roundf(fmaxf(-qmax, fminf(qmax, __fmul_rn(y[j], inv))));
+    __half sh = __float2half(s);
+    unsigned sbits = (unsigned)__half_as_ushort(sh);
+    if (lane == 0) *reinterpret_cast<unsigned short *>(page + (is_v ? g.vs_off : g.ks_off) + tok * 2) = (unsigned short)sbits;
+    if (DT == 1) {
+        if (!is_v) {
+            unsigned w = (unsigned)(c[0] & 0xFF) | ((unsigned)(c[1] & 0xFF) << 8) | ((unsigned)(c[2] & 0xFF) << 16) | ((unsigned)(c[3] & 0xFF) << 24);
+            *reinterpret_cast<unsigned *>(page + hy3a_k_dim_off<1>(tok, d0)) = w;
+        } else {
+            unsigned short u0 = (unsigned short)((c[0] & 0xFF) | ((c[1] & 0xFF) << 8));
+            unsigned short u1 = (unsigned short)((c[2] & 0xFF) | ((c[3] & 0xFF) << 8));
+            *reinterpret_cast<unsigned short *>(page + g.v_off + hy3a_v_unit_off<1>(tok, d0)) = u0;
+            *reinterpret_cast<unsigned short *>(page + g.v_off + hy3a_v_unit_off<1>(tok, d0 + 2)) = u1;
+        }
+    } else {
+        unsigned short u = (unsigned short)((c[0] & 0xF) | ((c[1] & 0xF) << 4) | ((c[2] & 0xF) << 8) | ((c[3] & 0xF) << 12));
+        int off = is_v ? g.v_off + hy3a_v_unit_off<2>(tok, d0) : hy3a_k_dim_off<2>(tok, d0);
+        *reinterpret_cast<unsigned short *>(page + off) = u;
+    }
+    return sbits;
+}
+
+struct append_args {
+    const float *q_in, *k_in, *v_in;
+    size_t q_stride, k_stride, v_stride;
+    float *q_out;
+    size_t q_out_stride;
+    __half *q_out16;
+    const float *norm_w; /* [2][128] for this layer */
+    float eps;
+    int layer;
+};
+
+/* grid (10, n_rows), block 256: warp (blockIdx.x*8 + warp) in [0,80) = 64 Q, 8 K, 8 V heads. */
+template <int DT>
+__global__ void __launch_bounds__(256) hy3a_append_kernel(hy3a_cache_view cache, hy3a_batch_view batch, hy3a_rope_params rope, append_args a) {
+    const int row = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hr = blockIdx.x * 8 + warp;
+    if (row >= batch.n || hr >= 80) return;
+    const hy3a_geom g = hy3a_make_geom(DT);
+    const int half = lane >> 4, idx = lane & 15;
+    const int d0 = half * 64 + idx * 4;
+    const int seq = batch.seq[row], slot = batch.slot[row], ti = batch.pos[row];
+
+    const bool is_q = hr < 64, is_k = (hr >= 64 && hr < 72);
+    const int head = is_q ? hr : (is_k ? hr - 64 : hr - 72);
+    const bool owned = is_q || (head >= cache.kv_head_begin && head < cache.kv_head_begin + cache.kv_heads);
+    if (!owned) return;
+    const float *src = is_q ? a.q_in + (size_t)row * a.q_stride : (is_k ? a.k_in + (size_t)row * a.k_stride : a.v_in + (size_t)row * a.v_stride);
+    float4 xv = *reinterpret_cast<const float4 *>(src + (size_t)head * HY3A_D + d0);
+    float y[4] = {xv.x, xv.y, xv.z, xv.w};
+
+    if (is_q || is_k) {
+        /* sum of squares, reference tree order */
+        float sq[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) sq[j] = __fmul_rn(y[j], y[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) sq[j] = __fadd_rn(sq[j], __shfl_xor_sync(0xffffffffu, sq[j], o));
+        }
+        float ss = __fadd_rn(__fadd_rn(sq[0], sq[2]), __fadd_rn(sq[1], sq[3]));
+        float r = rsqrtf(ss / (float)HY3A_D + a.eps);
+        const float *w = a.norm_w + (is_k ? HY3A_D : 0);
+        float4 wv = *reinterpret_cast<const float4 *>(w + d0);
+        y[0] = y[0] * r * wv.x; y[1] = y[1] * r * wv.y; y[2] = y[2] * r * wv.z; y[3] = y[3] * r * wv.w;
+        /* RoPE */
+        int pos = (ti + (ti >= rope.pos_jump_at ? rope.pos_jump : 0)) * rope.pos_stride;
+        float4 fv = *reinterpret_cast<const float4 *>(rope.inv_freq + idx * 4);
+        float fr4[4] = {fv.x, fv.y, fv.z, fv.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float other = __shfl_xor_sync(0xffffffffu, y[j], 16);
+            float fr = (float)pos * fr4[j];
+            float c = cosf(fr) * rope.attn_factor, s = sinf(fr) * rope.attn_factor;
+            float v0 = half ? other : y[j], v1 = half ? y[j] : other;
+            y[j] = half ? (v1 * c + v0 * s) : (v0 * c - v1 * s);
+        }
+    }
+    if (is_q) {
+        if (a.q_out) *reinterpret_cast<float4 *>(a.q_out + (size_t)row * a.q_out_stride + (size_t)head * HY3A_D + d0) = make_float4(y[0], y[1], y[2], y[3]);
+        if (a.q_out16) {
+            __half2 h01 = __floats2half2_rn(y[0], y[1]), h23 = __floats2half2_rn(y[2], y[3]);
+            uint2 w2;
+            w2.x = *reinterpret_cast<unsigned *>(&h01);
+            w2.y = *reinterpret_cast<unsigned *>(&h23);
+            *reinterpret_cast<uint2 *>(a.q_out16 + ((size_t)row * 64 + head) * HY3A_D + d0) = w2;
+        }
+        return;
+    }
+    const int hl = head - cache.kv_head_begin;
+    uint8_t *page = page_ptr(cache, seq, slot, a.layer, hl);
+    unsigned sb = store_row<DT>(page, g, slot & 127, !is_k, y, d0, lane);
+    if (DT != 0 && !is_k && lane == 0) atomicMax(cache.vs_max + a.layer * cache.kv_heads + hl, sb);
+}
+
+/* ---- device-side seeded fill (benchmark set-up) ----------------------------------- */
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+__device__ __forceinline__ float normal_from(unsigned long long r) {
+    float u1 = ((float)((r >> 40) & 0xFFFFFFull) + 1.0f) * (1.0f / 16777217.0f);
+    float u2 = (float)((r >> 8) & 0xFFFFFFull) * (1.0f / 16777216.0f);
+    return sqrtf(-2.0f * __logf(u1)) * __cosf(6.283185307179586f * u2);
+}
+/* grid (2, n): block 256 = 8 warps = the 8 heads of K (blockIdx.x 0) or V (1) of one token. */
+template <int DT>
+__global__ void __launch_bounds__(256) hy3a_fill_random_kernel(hy3a_cache_view cache, int layer, int seq, int t0, int n, unsigned long long seed) {
+    const int t = t0 + blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool is_v = blockIdx.x == 1;
+    if (blockIdx.y >= n || warp >= cache.kv_heads) return;
+    const hy3a_geom g = hy3a_make_geom(DT);
+    const int half = lane >> 4, idx = lane & 15, d0 = half * 64 + idx * 4;
+    float y[4];
+    unsigned long long base = seed ^ ((unsigned long long)(layer * 2 + (is_v ? 1 : 0) + 1) << 40);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        unsigned long long index = ((unsigned long long)t * 8ull + (unsigned long long)(warp + cache.kv_head_begin)) * 128ull + (unsigned long long)(d0 + j);
+        y[j] = normal_from(splitmix64(base ^ (index + ((unsigned long long)seq << 34))));
+    }
+    uint8_t *page = page_ptr(cache, seq, t, layer, warp);
+    unsigned sb = store_row<DT>(page, g, t & 127, is_v, y, d0, lane);
+    if (DT != 0 && is_v && lane == 0) atomicMax(cache.vs_max + layer * cache.kv_heads + warp, sb);
+}
+
+/* ---- import / export in the reference's slot format ---------------------------------
+ * One thread per (token, head, 4-dim group).  import=0: page -> slot, import=1: slot -> page. */
+template <int DT>
+__global__ void hy3a_xport_kernel(hy3a_cache_view cache, int layer, int seq, int t0, int n, uint8_t *kslots, uint8_t *vslots, int import) {
+    const hy3a_geom g = hy3a_make_geom(DT);
+    const int slot_bytes = DT == 1 ? 1040 : (DT == 2 ? 528 : 2048);
+    const int hdr = DT == 0 ? 0 : 16;
+    const int head_bytes = DT == 1 ? 128 : (DT == 2 ? 64 : 256);
+    long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long total = (long long)n * 8 * 32 * 2;
+    if (gid >= total) return;
+    int is_v = (int)(gid & 1); gid >>= 1;
+    int q4 = (int)(gid & 31); gid >>= 5;
+    int head = (int)(gid & 7); gid >>= 3;
+    int ti = (int)gid, t = t0 + ti;
+    uint8_t *slot = (is_v ? vslots : kslots) + (size_t)ti * slot_bytes;
+    int hl = head - cache.kv_head_begin;
+    bool owned = hl >= 0 && hl < cache.kv_heads;
+    int d0 = q4 * 4;
+    int sbytes = DT == 1 ? 4 : (DT == 2 ? 2 : 8); /* bytes of 4 dims in slot format */
+    uint8_t *sp = slot + hdr + head * head_bytes + (DT == 1 ? d0 : (DT == 2 ? d0 / 2 : d0 * 2));
+    if (!owned) {
+        if (!import) { for (int b = 0; b < sbytes; b++) sp[b] = 0; if (DT != 0 && q4 == 0) { slot[head * 2] = 0; slot[head * 2 + 1] = 0; } }
+        return;
+    }
+    uint8_t *page = page_ptr(cache, seq, t, layer, hl);
+    int tok = t & 127;
+    /* byte locations of these 4 dims inside the page */
+    uint8_t *pp[8];
+    if (DT == 0) { int off = is_v ? g.v_off + hy3a_v16_dim_off(tok, d0) : hy3a_k_dim_off<0>(tok, d0); for (int b = 0; b < 8; b++) pp[b] = page + off + b; }
+    else if (DT == 1) {
+        if (!is_v) { int off = hy3a_k_dim_off<1>(tok, d0); for (int b = 0; b < 4; b++) pp[b] = page + off + b; }
+        else { int o0 = g.v_off + hy3a_v_unit_off<1>(tok, d0), o1 = g.v_off + hy3a_v_unit_off<1>(tok, d0 + 2); pp[0] = page + o0; pp[1] = page + o0 + 1; pp[2] = page + o1; pp[3] = page + o1 + 1; }
+    } else {
+        int off = is_v ? g.v_off + hy3a_v_unit_off<2>(tok, d0) : hy3a_k_dim_off<2>(tok, d0); pp[0] = page + off; pp[1] = page + off + 1;
+    }
+    for (int b = 0; b < sbytes; b++) { if (import) *pp[b] = sp[b]; else sp[b] = *pp[b]; }
+    if (DT != 0 && q4 == 0) {
+        uint8_t *sc = page + (is_v ? g.vs_off : g.ks_off) + tok * 2;
+        if (import) {
+            sc[0] = slot[head * 2]; sc[1] = slot[head * 2 + 1];
+            if (is_v) atomicMax(cache.vs_max + layer * cache.kv_heads + hl, (unsigned)slot[head * 2] | ((unsigned)slot[head * 2 + 1] << 8));
+        } else { slot[head * 2] = sc[0]; slot[head * 2 + 1] = sc[1]; }
+    }
+}
+
+} /* namespace */
+
+int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, const float *k_in, size_t k_stride,
+                       const float *v_in, size_t v_stride, float *q_out, size_t q_out_stride, void *q_out16) {
+    append_args a;
+    a.q_in = q_in; a.k_in = k_in; a.v_in = v_in; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
+    a.q_out = q_out; a.q_out_stride = q_out_stride; a.q_out16 = (__half *)q_out16;
+    a.norm_w = ctx->d_norm_w + (size_t)layer * 2 * HY3A_D; a.eps = ctx->cfg.rms_eps; a.layer = layer;
+    dim3 grid(10, ctx->batch_n), block(256);
+    hy3a_cache_view cv = hy3a_view(ctx);
+    hy3a_batch_view bv = hy3a_bview(ctx);
+    switch (ctx->cfg.kv_dtype) {
+        case 0: hy3a_append_kernel<0><<<grid, block, 0, ctx->stream>>>(cv, bv, ctx->rope, a); break;
+        case 1: hy3a_append_kernel<1><<<grid, block, 0, ctx->stream>>>(cv, bv, ctx->rope, a); break;
+        default: hy3a_append_kernel<2><<<grid, block, 0, ctx->stream>>>(cv, bv, ctx->rope, a); break;
+    }
+    ctx->launches++;
+    HY3A_CUDA(ctx, cudaGetLastError());
+    return HY3A_OK;
+}
+
+int hy3a_launch_fill_random(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint64_t seed) {
+    hy3a_cache_view cv = hy3a_view(ctx);
+    for (int done = 0; done < n;) {
+        int chunk = n - done > 32768 ? 32768 : n - done;
+        dim3 grid(2, chunk), block(256);
+        switch (ctx->cfg.kv_dtype) {
+            case 0: hy3a_fill_random_kernel<0><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0 + done, chunk, seed); break;
+            case 1: hy3a_fill_random_kernel<1><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0 + done, chunk, seed); break;
+            default: hy3a_fill_random_kernel<2><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0 + done, chunk, seed); break;
+        }
+        ctx->launches++;
+        HY3A_CUDA(ctx, cudaGetLastError());
+        done += chunk;
+    }
+    return HY3A_OK;
+}
+
+int hy3a_launch_export(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint8_t *d_kslots, uint8_t *d_vslots, int import) {
+    hy3a_cache_view cv = hy3a_view(ctx);
+    long long total = (long long)n * 8 * 32 * 2;
+    int block = 256;
+    unsigned grid = (unsigned)((total + block - 1) / block);
+    switch (ctx->cfg.kv_dtype) {
+        case 0: hy3a_xport_kernel<0><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0, n, d_kslots, d_vslots, import); break;
+        case 1: hy3a_xport_kernel<1><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0, n, d_kslots, d_vslots, import); break;
+        default: hy3a_xport_kernel<2><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0, n, d_kslots, d_vslots, import); break;
+    }
+    ctx->launches++;
+    HY3A_CUDA(ctx, cudaGetLastError());
+    return HY3A_OK;
+}

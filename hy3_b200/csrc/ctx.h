@@ -1,0 +1,120 @@
+/* ctx.h -- the context object behind the C ABI, and the parameter blocks of the kernels. */
+#ifndef HY3A_CTX_H
+#define HY3A_CTX_H
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/hy3_attn.h"
+#include "layout.h"
+
+#define HY3A_MAX_LAYERS 128
+#define HY3A_DECODE_WARPS 8
+#define HY3A_ERR_WORDS 4
+#define HY3A_RING_SLOTS 16
+
+/* Everything a kernel needs to address the cache; passed by value. */
+struct hy3a_cache_view {
+    uint8_t *pool;           /* base of the block pool */
+    const int *block_table;  /* [max_seqs][max_blocks_per_seq] */
+    int max_blocks_per_seq;
+    int n_layers;
+    int kv_heads;            /* owned KV heads */
+    int kv_head_begin;
+    int page_bytes;
+    unsigned int *vs_max;    /* [n_layers][kv_heads] running max of V scale bits (fp16 as uint) */
+};
+
+__host__ __device__ __forceinline__ size_t hy3a_page_index(const hy3a_cache_view &c, int block, int layer, int head_local) {
+    return ((size_t)block * c.n_layers + layer) * c.kv_heads + head_local;
+}
+
+/* Per-step batch descriptor, device resident (struct of arrays in one allocation). */
+struct hy3a_batch_view {
+    const int *seq;   /* [n] */
+    const int *slot;  /* [n] */
+    const int *pos;   /* [n] */
+    int n;
+};
+
+struct hy3a_rope_params {
+    const float *inv_freq; /* device float[64] */
+    float attn_factor;
+    int pos_stride, pos_jump, pos_jump_at;
+};
+
+struct hy3a_ctx {
+    hy3a_config cfg;
+    hy3a_geom geom;
+    int device;
+    int sm_count;
+    cudaStream_t stream;
+    int own_stream;
+
+    /* device memory */
+    uint8_t *pool;
+    size_t pool_bytes;
+    int *d_block_table;
+    unsigned int *d_vs_max;
+    float *d_inv_freq;
+    float *d_norm_w;      /* [n_layers][2][128] */
+    int *d_batch;         /* [3][max_batch] seq, slot, pos */
+    float *d_partials;    /* decode scratch: [(ctas + max_batch*kv_heads)][8][130] */
+    unsigned int *d_counters; /* decode scratch: [max_batch*kv_heads] arrival counters (self-resetting) */
+    void *d_pf_k, *d_pf_v; /* prefill: fp16 staging of dequantised K / V pages (INT8/INT4 caches) */
+    size_t pf_bytes;
+    unsigned int *d_err;  /* HY3A_ERR_WORDS words: kernels record bounded-wait timeouts / bad indices here */
+    size_t partial_records;
+
+    /* host mirrors */
+    int *h_block_table;   /* [max_seqs][max_blocks_per_seq], -1 = unmapped */
+    int *h_seq_blocks;    /* [max_seqs] mapped block count */
+    int *h_free;          /* free-list stack */
+    int n_free;
+    char *h_ring;         /* pinned staging ring for small host->device copies */
+    size_t ring_slot_bytes;
+    cudaEvent_t ring_ev[HY3A_RING_SLOTS];
+    int ring_used[HY3A_RING_SLOTS];
+    int ring_next;
+    unsigned int *h_err;  /* pinned */
+    int batch_n;
+    int decode_ctas;
+
+    hy3a_rope_params rope;
+    uint64_t launches;
+    char err[512];
+};
+
+/* internal kernel launchers (defined in the .cu files) */
+int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, const float *k_in, size_t k_stride,
+                       const float *v_in, size_t v_stride, float *q_out, size_t q_out_stride, void *q_out16);
+int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride,
+                       float *partials);
+int hy3a_launch_merge(hy3a_ctx *ctx, const float *partials, int n_parts, int n_rows, int n_heads, float *out,
+                      size_t out_stride);
+int hy3a_launch_export(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint8_t *d_kslots, uint8_t *d_vslots, int import);
+int hy3a_launch_fill_random(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint64_t seed);
+int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq, const void *q16, float *out,
+                        size_t out_stride);
+int hy3a_fail(hy3a_ctx *ctx, int code, const char *fmt, ...);
+
+static inline hy3a_cache_view hy3a_view(const hy3a_ctx *c) {
+    hy3a_cache_view v;
+    v.pool = c->pool; v.block_table = c->d_block_table; v.max_blocks_per_seq = c->cfg.max_blocks_per_seq;
+    v.n_layers = c->cfg.n_layers; v.kv_heads = c->cfg.kv_head_count; v.kv_head_begin = c->cfg.kv_head_begin;
+    v.page_bytes = c->geom.page_bytes; v.vs_max = c->d_vs_max;
+    return v;
+}
+static inline hy3a_batch_view hy3a_bview(const hy3a_ctx *c) {
+    hy3a_batch_view b;
+    b.seq = c->d_batch; b.slot = c->d_batch + c->cfg.max_batch; b.pos = c->d_batch + 2 * c->cfg.max_batch; b.n = c->batch_n;
+    return b;
+}
+
+#define HY3A_CUDA(ctx, call)                                                                                   \
+    do {                                                                                                       \
+        cudaError_t e_ = (call);                                                                               \
+        if (e_ != cudaSuccess) return hy3a_fail((ctx), HY3A_ECUDA, "%s: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+#endif
