@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the Hy3 attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): decode attention with an INT8 KV cache, batch 1, 80 independent layer caches of
+32768 positions each, 64 query heads over 8 KV heads, head_dim 128.  One STEP = one new token:
+for each of the 80 layers the fused QK-RMSNorm + RoPE + quantise/append kernel stores the token,
+then the split-KV decode kernel attends over all positions (32768 + steps so far).  The 160
+launches of a step are replayed as one CUDA graph; lengths live in device memory.
+Metric: decode attention KV GB/s = algorithmic KV bytes read per step (ntok x 2080 B per layer,
+i.e. codes + fp16 scales of K and V) / time.  Synthetic seeded N(0,1) data, random "weights".
+
+N>1 (weak scaling): every rank holds 32768 positions per layer of ONE sequence of 32768*N tokens
+(sequence sharding); per layer each rank emits {m,l,acc} partials, one NCCL all-gather, local merge.
+
+--impl reference: the reference engine's own CPU attention() (hy3.c:617-652, compiled from the
+reference sources into oracle/_ref; falls back to the C restatement in oracle/) on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_LAYERS, NTOK, H, G, D = 80, 32768, 64, 8, 128
+INT8_BYTES_PER_TOKEN_LAYER = 2 * G * (D + 2)       # 2080: K and V, 8 heads x (128 codes + fp16 scale)
+SEED = 0x4859335F53454544
+METRIC, UNIT = "decode_attn_kv_GBps", "GB/s"
+WORKLOAD = ("configs[1]: INT8-KV decode attention, batch 1, 80 independent layer caches x 32768 positions, "
+            "64 Q / 8 KV heads, head_dim 128, one token appended per layer per step (fused norm+RoPE+quantise), 1 GPU")
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p))["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) >= 9:
+                for nme, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nme)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------- CPU arms
+def cpu_attention_sample(seconds, all_threads):
+    """Time the reference CPU attention on a bounded sample of the workload.  Returns a dict with the
+    metric value in GB/s of INT8-equivalent KV bytes (tokens x 2080 B), so it is the same unit of work."""
+    import numpy as np
+    import oracle
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(1)
+    if oracle.ref_cpu is not None:
+        ntok = 4096           # hy3.c:628-629 caps the reference at 4096 keys; longer inputs are silently truncated
+        nl = max(1, min(N_LAYERS, cores // 8 * 2 if all_threads else 1)) if all_threads else 1
+        K = rng.standard_normal((ntok, G, D)).astype(np.float32)
+        V = rng.standard_normal((ntok, G, D)).astype(np.float32)
+        for l in range(nl):
+            oracle.ref_cpu.load_layer(K, V, l)
+        q = rng.standard_normal((nl, H, D)).astype(np.float32)
+        if all_threads:
+            fn = lambda: oracle.ref_cpu.attention_layers(q, ntok)
+            threads = min(cores, nl * 8, oracle.ref_cpu.max_threads())
+        else:
+            fn = lambda: oracle.ref_cpu.attention(q[0], ntok, 0)
+            threads = 1
+        kind = "reference"
+        sample = ("hy3.c attention() as shipped (-O3 -ffast-math), fp32 KV, %d layer(s) x first %d of 32768 positions "
+                  "(the reference caps at 4096 keys), %d thread(s)" % (nl, ntok, threads))
+    else:
+        ntok, nl, threads, kind = NTOK, 1, 1, "port"
+        K = rng.standard_normal((ntok, G, D)).astype(np.float32)
+        V = rng.standard_normal((ntok, G, D)).astype(np.float32)
+        q = rng.standard_normal((1, H, D)).astype(np.float32)
+        fn = lambda: oracle.attention(q[0], K, V)
+        sample = "C restatement of hy3.c attention(), fp32 KV, 1 layer x 32768 positions, 1 thread"
+    fn()
+    times = []
+    t_end = time.perf_counter() + seconds
+    while time.perf_counter() < t_end or len(times) < 3:
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    best = statistics.median(times)
+    gbs = nl * ntok * INT8_BYTES_PER_TOKEN_LAYER / best / 1e9
+    return {"value": gbs, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample,
+            "ms_per_call": best * 1e3, "host_cores": cores, "fp32_kv_GBps": nl * ntok * 2 * G * D * 4 / best / 1e9,
+            "layers": nl, "ntok": ntok}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = None
+    base = cpu_attention_sample(0.0, True)        # warm + shape
+    import oracle  # noqa: F401
+    # one "step" = one pass of the bounded sample; W warm-up, K timed
+    import numpy as np  # noqa: F401
+    times = []
+    for i in range(args.warmup + args.steps):
+        r = cpu_attention_sample(0.0, True)
+        if i >= args.warmup:
+            times.append(r["ms_per_call"])
+    per_step = sum(times) / len(times)
+    value = base["layers"] * base["ntok"] * INT8_BYTES_PER_TOKEN_LAYER / (per_step / 1e3) / 1e9
+    cb = {k: base[k] for k in ("unit", "cores", "kind", "sample")}
+    cb["value"] = value
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD},
+                      "cpu_baseline": cb, "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "gpu_launches": 0}))
+
+
+# ------------------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from hy3_b200 import Hy3Attn
+    from hy3_b200.sharding import make_cuda_sharded_decode
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    total_steps = args.warmup + args.steps + 8
+    n_layers = args.layers
+    ntok0 = args.ntok
+    ctx = Hy3Attn(kv_dtype=args.kv, n_layers=n_layers, max_batch=1, max_tokens=ntok0 + total_steps + 256, device=local)
+    stream = torch.cuda.Stream(device=dev)
+    ctx.set_stream(stream)
+    rng = np.random.default_rng(7)
+    for l in range(n_layers):
+        w = (1.0 + 0.02 * rng.standard_normal((2, 128))).astype(np.float32)
+        ctx.set_norm_weights(l, w[0], w[1])
+        ctx.fill_random(l, 0, 0, ntok0, SEED + 1000 * rank)
+    ctx.sync()
+    bytes_per_token = {"int8": 2080, "int4": 1056, "fp16": 4096}[args.kv]
+
+    # per-step inputs: the new token's pre-norm q | k | v for every layer, [80][10240] fp32 (reference row layout)
+    ROW = H * D + 2 * G * D
+    host_in = torch.randn((n_layers, ROW), dtype=torch.float32).pin_memory()
+    host_out = torch.empty((n_layers, H * D), dtype=torch.float32).pin_memory()
+    with torch.cuda.stream(stream):
+        x = host_in.to(dev, non_blocking=True)
+        qo = torch.empty((n_layers, 1, H, D), dtype=torch.float32, device=dev)
+        out = torch.zeros((n_layers, 1, H, D), dtype=torch.float32, device=dev)
+    owner = (rank == world - 1)                      # sequence sharding: the tail rank appends the new token
+    sharded = make_cuda_sharded_decode(ctx, 1) if world > 1 else None
+
+    def layer_views(l):
+        row = x[l]
+        return (row[:H * D].view(1, H, D), row[H * D:H * D + G * D].view(1, G, D), row[H * D + G * D:].view(1, G, D))
+
+    def enqueue_step():
+        """All launches of one step on `stream` (captured into a graph once)."""
+        for l in range(n_layers):
+            q, k, v = layer_views(l)
+            if owner:
+                ctx.append(l, q, k, v, q_out=qo[l])
+            else:
+                ctx.append(l, q, None, None, q_out=qo[l])   # only the rotated query is needed on this rank
+            if sharded is None:
+                ctx.decode(l, qo[l], out=out[l])
+            else:
+                sharded.step(l, qo[l], out[l])
+
+    def set_positions(step):
+        local_slot = ntok0 + step if owner else ntok0 - 1
+        global_pos = (ntok0 * world + step) if world > 1 else local_slot
+        ctx.batch_set([0], [local_slot], [global_pos])
+
+    stream.synchronize()
+    launches_before = ctx.launches
+    set_positions(0)
+    with torch.cuda.stream(stream):
+        enqueue_step()                                # eager warm-up (also warms NCCL)
+    stream.synchronize()
+    per_step_launches = ctx.launches - launches_before
+    graph = torch.cuda.CUDAGraph()
+    set_positions(1)
+    with torch.cuda.graph(graph, stream=stream):
+        enqueue_step()
+    stream.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- (1) device-resident throughput: W warm-up + K timed graph replays
+    step_no = 2
+    for _ in range(args.warmup):
+        set_positions(step_no); step_no += 1
+        with torch.cuda.stream(stream):
+            graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_step = step_no
+    e0.record(stream)
+    for _ in range(args.steps):
+        set_positions(step_no); step_no += 1
+        with torch.cuda.stream(stream):
+            graph.replay()
+    e1.record(stream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    ctx.sync()
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    tokens_attended = sum(ntok0 + s + 1 for s in range(first_step, first_step + args.steps)) / args.steps  # per layer per step
+    bytes_per_step = n_layers * tokens_attended * bytes_per_token * world
+    value = bytes_per_step / (ms_per_step / 1e3) / 1e9
+
+    # ---- (2) end to end through the public API with HOST buffers (pinned), copies inside the timed region
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        set_positions(step_no); step_no += 1
+        with torch.cuda.stream(stream):
+            x.copy_(host_in, non_blocking=True)
+            graph.replay()
+            host_out.copy_(out.view(n_layers, H * D), non_blocking=True)
+        stream.synchronize()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = bytes_per_step / (e2e_ms / 1e3) / 1e9
+
+    # ---- (3) the dominant kernel alone: decode launches cycling over the layers (each layer's cache is
+    #          68 MB and the 80 of them 5.45 GB >> 126 MB L2), CUDA events on the launching stream
+    set_positions(step_no)
+    reps = max(1, 240 // n_layers)
+    with torch.cuda.stream(stream):
+        for l in range(min(n_layers, 8)):
+            ctx.decode(l, qo[l], out=out[l])
+        e0.record(stream)
+        for _ in range(reps):
+            for l in range(n_layers):
+                ctx.decode(l, qo[l], out=out[l])
+        e1.record(stream)
+    stream.synchronize()
+    k_ms = e0.elapsed_time(e1) / (reps * n_layers)
+    k_bytes = (ntok0 + step_no + 1) * bytes_per_token
+    peak, peak_src = peaks()
+    achieved = k_bytes / (k_ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "hy3a_decode_kernel<%s>" % args.kv, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0, "peak_source": peak_src,
+                "us_per_launch": k_ms * 1e3, "algorithmic_bytes_per_launch": k_bytes, "traffic": None}
+    tr = os.path.join(ROOT, "profiles", "decode_%s_traffic.json" % args.kv)
+    if os.path.exists(tr):
+        t = json.load(open(tr))
+        roofline["traffic"] = t["dram_bytes_per_token_kvhead_layer"] * (ntok0 + step_no + 1) * G
+        roofline["traffic_source"] = t["source"]
+    ctx.sync()
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            cpu = cpu_attention_sample(args.cpu_seconds, False)
+            cpu_mt = cpu_attention_sample(min(args.cpu_seconds, 5.0), True)
+            cpu["all_threads"] = {k: cpu_mt[k] for k in ("value", "cores", "sample", "ms_per_call")}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic",
+                "config": {"workload": WORKLOAD if (world == 1 and args.kv == "int8" and n_layers == N_LAYERS and ntok0 == NTOK)
+                           else "%s-KV decode, %d layers x %d positions per GPU, %d GPU(s)%s" % (
+                               args.kv, n_layers, ntok0, world, ", sequence-sharded with NCCL all-gather LSE merge" if world > 1 else ""),
+                           "kv_dtype": args.kv, "layers": n_layers, "positions_per_gpu": ntok0, "compute": "fp16 mma.sync, fp32 accumulate/softmax",
+                           "l2": "inputs larger than L2: %.2f GB of KV streamed per step, every layer's cache read once" % (bytes_per_step / world / 1e9),
+                           "graph": "one CUDA graph of %d launches per step" % per_step_launches},
+                "frac_of_hbm_peak": value / world / peak, "roofline": roofline, "cpu_baseline": cpu,
+                "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_in.numel() * 4,
+                        "d2h_bytes_per_step": host_out.numel() * 4},
+                "gpu_launches": per_step_launches * args.steps, "clocks": clocks}
+        print(json.dumps(line))
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kv", default="int8", choices=["int8", "int4", "fp16"])
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--ntok", type=int, default=NTOK)
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -41,6 +41,7 @@ class Hy3Attn:
         if rc:
             raise Hy3AttnError(rc, self.lib.hy3a_last_error(None).decode())
         self.h = h
+        self.batch_n = 0
         if stream is not None:
             self.set_stream(stream)
 
@@ -120,14 +121,15 @@ class Hy3Attn:
         """q [n,64,128] / k,v [n,8,128] fp32 (row stride free, rows dense).  Returns q_out (fp32)."""
         import torch
         n = self.batch_n
-        assert q.shape[0] == n and k.shape[0] == n and v.shape[0] == n
+        assert (k is None) == (v is None)
         for t in (q, k, v):
-            assert t.dtype == torch.float32 and t.stride(-1) == 1 and t.stride(-2) == D
+            assert t is None or (t.shape[0] == n and t.dtype == torch.float32 and t.stride(-1) == 1 and t.stride(-2) == D)
         if q_out is None:
             q_out = torch.empty((n, H, D), dtype=torch.float32, device=q.device)
         if q_out16 is not None:
             assert q_out16.dtype == torch.float16 and q_out16.is_contiguous() and q_out16.numel() == n * H * D
-        self._chk(self.lib.hy3a_append(self.h, layer, _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0),
+        self._chk(self.lib.hy3a_append(self.h, layer, _ptr(q), q.stride(0), _ptr(k), 0 if k is None else k.stride(0),
+                                       _ptr(v), 0 if v is None else v.stride(0),
                                        _ptr(q_out), q_out.stride(0), _ptr(q_out16)))
         return q_out
 

@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(256) hy3a_append_kernel(hy3a_cache_view cache,
     const bool is_q = hr < 64, is_k = (hr >= 64 && hr < 72);
     const int head = is_q ? hr : (is_k ? hr - 64 : hr - 72);
     const bool owned = is_q || (head >= cache.kv_head_begin && head < cache.kv_head_begin + cache.kv_heads);
-    if (!owned) return;
+    if (!owned || (!is_q && a.k_in == nullptr)) return; /* k_in == NULL: query-only mode */
     const float *src = is_q ? a.q_in + (size_t)row * a.q_stride : (is_k ? a.k_in + (size_t)row * a.k_stride : a.v_in + (size_t)row * a.v_stride);
     float4 xv = *reinterpret_cast<const float4 *>(src + (size_t)head * HY3A_D + d0);
     float y[4] = {xv.x, xv.y, xv.z, xv.w};

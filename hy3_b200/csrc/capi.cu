@@ -72,7 +72,9 @@ int hy3a_decode_schedule(int n, const int *kv_lens, int kv_heads, int n_ctas, in
     long long pages = 0;
     for (int i = 0; i < n; i++) pages += kv_lens[i] > 0 ? (kv_lens[i] + HY3A_PAGE_TOKENS - 1) / HY3A_PAGE_TOKENS : 0;
     long long U = pages * kv_heads;
+    if (U < n_ctas) n_ctas = (int)U;   /* the kernel never uses more CTAs than units */
     if (total_units) *total_units = U;
+    if (cta >= n_ctas) { if (u0) *u0 = U; if (u1) *u1 = U; return 0; }
     if (u0) *u0 = (long long)cta * U / n_ctas;
     if (u1) *u1 = (long long)(cta + 1) * U / n_ctas;
     return 0;
@@ -331,7 +333,7 @@ int hy3a_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, co
                 size_t v_stride, float *q_out, size_t q_out_stride, void *q_out16) {
     int rc = check_layer(ctx, layer, "append");
     if (rc) return rc;
-    if (!q_in || !k_in || !v_in) return hy3a_fail(ctx, HY3A_EINVAL, "append: NULL input");
+    if (!q_in || (!k_in) != (!v_in)) return hy3a_fail(ctx, HY3A_EINVAL, "append: NULL input (k_in and v_in may only be NULL together)");
     if (((uintptr_t)q_in | (uintptr_t)k_in | (uintptr_t)v_in | (uintptr_t)q_out | (uintptr_t)q_out16) & 15)
         return hy3a_fail(ctx, HY3A_EINVAL, "append: pointers must be 16-byte aligned");
     if ((q_stride | k_stride | v_stride | q_out_stride) & 3) return hy3a_fail(ctx, HY3A_EINVAL, "append: strides must be multiples of 4 floats");

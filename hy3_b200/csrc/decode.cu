@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tig = lane & 3;
     const int n = batch.n, G = cache.kv_heads;
-    const int C = gridDim.x, cta = blockIdx.x;
+    const int cta = blockIdx.x;
     int *s_prefix = s_dyn;
 
     /* ---- schedule: prefix of pages per row */
@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
     __syncthreads();
 
     /* rows with no keys on this rank: zero output / empty partial (hy3_gpu.cu:197-199) */
-    for (int i = cta; i < n; i += C) {
+    for (int i = cta; i < n; i += gridDim.x) {
         if (s_prefix[i + 1] != s_prefix[i]) continue;
         for (int e = tid; e < G * 8 * HY3A_D; e += kThreads) {
             int hq = e / HY3A_D, d = e % HY3A_D;
@@ -192,7 +192,10 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
     }
 
     const long long U = (long long)G * s_prefix[n];
-    if (U == 0) return;
+    /* never more CTAs than units, so that every participating CTA owns at least one unit and the
+     * CTAs that share a segment are exactly the contiguous range [c_first, c_last]              */
+    const int C = (long long)gridDim.x < U ? (int)gridDim.x : (int)U;
+    if (cta >= C) return;
     const long long u_begin = (long long)cta * U / C, u_end = (long long)(cta + 1) * U / C;
 
     /* per-thread page-relative offsets (loop invariant) */

@@ -1,0 +1,101 @@
+"""Multi-GPU decode, one process per GPU (torch.distributed over NCCL for the exchange).
+
+Two partitions of the attention path, neither present in the single-GPU reference:
+
+* by KV head  -- rank r owns KV heads [r*8/W, (r+1)*8/W) of every cache and the matching query
+  heads; attention needs NO collective, outputs stay head-sharded (kv_head_range()).
+* by sequence -- rank r holds a contiguous token range of every sequence; each rank runs the same
+  split-KV kernel over its range and emits one unnormalised {m, l, acc[128]} record per head (the
+  record of hy3_gpu.cu:183-230); ONE all-gather of those records per layer-step and a local fold in
+  rank order with the rule of attention_reduce_kernel (hy3_gpu.cu:233-247) gives every rank the same
+  bits.  The newest token is appended on the rank that owns the tail of the sequence only.
+
+The compute callables are injected so that the exchange logic can run on CPU ranks (gloo) in tests.
+"""
+import numpy as np
+
+PARTIAL_FLOATS = 130
+
+
+def kv_head_range(rank, world, n_kv_heads=8):
+    """(first KV head, count) owned by `rank`; world must divide 8."""
+    if n_kv_heads % world:
+        raise ValueError("world size %d does not divide %d KV heads" % (world, n_kv_heads))
+    per = n_kv_heads // world
+    return rank * per, per
+
+
+def sequence_range(rank, world, ntok, align=128):
+    """Contiguous, page-aligned token range [t0, t1) of a sequence of ntok tokens owned by `rank`.
+    Ranges are cut at multiples of `align`; the last rank takes the remainder (and new tokens)."""
+    pages = (ntok + align - 1) // align
+    per = pages // world
+    extra = pages % world
+    p0 = rank * per + min(rank, extra)
+    p1 = p0 + per + (1 if rank < extra else 0)
+    return min(p0 * align, ntok), min(p1 * align, ntok)
+
+
+class SequenceShardedDecode:
+    """Per-layer decode step of a sequence-sharded cache: local partials -> all-gather -> merge."""
+
+    def __init__(self, partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty_like):
+        """partial_fn(layer, q, partial_buf): fill [n_rows, n_heads, 130] for the local token range;
+        merge_fn(gathered, n_parts, out): fold [world, n_rows, n_heads, 130] in rank order;
+        all_gather_fn(gathered, local): the collective; empty_like(shape): buffer factory."""
+        self.partial_fn, self.merge_fn, self.all_gather_fn = partial_fn, merge_fn, all_gather_fn
+        self.world, self.n_rows, self.n_heads = world, n_rows, n_heads
+        self.local = empty_like((n_rows, n_heads, PARTIAL_FLOATS))
+        self.gathered = empty_like((world, n_rows, n_heads, PARTIAL_FLOATS))
+
+    def step(self, layer, q, out):
+        self.partial_fn(layer, q, self.local)
+        if self.world == 1:
+            self.merge_fn(self.local, 1, out)
+        else:
+            self.all_gather_fn(self.gathered, self.local)
+            self.merge_fn(self.gathered, self.world, out)
+        return out
+
+
+def make_cuda_sharded_decode(ctx, n_rows, group=None):
+    """Wire SequenceShardedDecode to a Hy3Attn context and torch.distributed (NCCL)."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    dev = torch.device("cuda", torch.cuda.current_device())
+    n_heads = 8 * ctx.kv_head_count
+
+    def partial_fn(layer, q, buf):
+        ctx.decode(layer, q, partials=buf)
+
+    def merge_fn(gathered, n_parts, out):
+        ctx.merge_partials(gathered, n_parts, n_rows, n_heads, out)
+
+    def all_gather_fn(gathered, local):
+        dist.all_gather_into_tensor(gathered, local, group=group)
+
+    def empty(shape):
+        return torch.empty(shape, dtype=torch.float32, device=dev)
+
+    return SequenceShardedDecode(partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty)
+
+
+def merge_partials_numpy(gathered):
+    """Reference fold used by CPU tests of the exchange logic: [W, rows, heads, 130] -> [rows, heads, 128]."""
+    W, R, Hn, _ = gathered.shape
+    out = np.zeros((R, Hn, 128), np.float32)
+    for r in range(R):
+        for h in range(Hn):
+            ms, ss, ov = -np.inf, np.float32(0), np.zeros(128, np.float32)
+            for s in range(W):
+                pm, pl = gathered[s, r, h, 0], gathered[s, r, h, 1]
+                if not pl > 0:
+                    continue
+                nm = max(ms, pm)
+                os_, rs = np.float32(np.exp(ms - nm)), np.float32(np.exp(pm - nm))
+                ss = ss * os_ + pl * rs
+                ov = ov * os_ + gathered[s, r, h, 2:] * rs
+                ms = nm
+            out[r, h] = ov / ss if ss > 0 else 0
+    return out

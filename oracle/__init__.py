@@ -241,6 +241,13 @@ class _RefCpu:
         fn(_p(out), _p(q), C.c_int(ntok), C.c_int(layer))
         return out
 
+    def attention_layers(self, q, ntok):
+        """q [n_layers, 64, 128]; all layers previously loaded with load_layer; all host threads."""
+        q = _f32(q)
+        out = np.zeros_like(q)
+        self.lib.hy3ref_attention_layers_mt(_p(out), _p(q), C.c_int(ntok), C.c_int(q.shape[0]))
+        return out
+
     def max_threads(self):
         return int(self.lib.hy3ref_max_threads())
 

@@ -76,6 +76,15 @@ void hy3ref_attention_mt(float *out, const float *q, int ntok, int layer) {
     for (int g = 0; g < HY3_N_KV_HEAD; g++) hy3ref_attention_group(out, q, ntok, layer, g);
 }
 
+/* Several layers of the loaded slot arrays at once: (layer, group) pairs spread over all
+ * OpenMP threads, each pair one call of the unmodified attention().  q/out: [n_layers][64][128]. */
+void hy3ref_attention_layers_mt(float *out, const float *q, int ntok, int n_layers) {
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int l = 0; l < n_layers; l++)
+        for (int g = 0; g < HY3_N_KV_HEAD; g++)
+            hy3ref_attention_group(out + (size_t)l * HY3_N_HEAD * HY3_HEAD_DIM, q + (size_t)l * HY3_N_HEAD * HY3_HEAD_DIM, ntok, l, g);
+}
+
 void hy3ref_rms_norm(float *out, const float *x, const float *w, int n, float eps) { rms_norm(out, x, w, n, eps); }
 
 /* hy3_rope_init on a zeroed model (no GGUF: every metadata lookup falls back to

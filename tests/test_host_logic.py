@@ -17,7 +17,9 @@ def test_schedule_partitions_units(lens, heads, ctas):
         prev = u1
         sizes.append(u1 - u0)
     assert prev == total
-    assert max(sizes) - min(sizes) <= 1          # balanced to one page
+    active = [x for x in sizes[:min(ctas, total)]]
+    assert not active or (max(active) - min(active) <= 1 and min(active) >= 1)   # balanced to one page, no idle CTA inside
+    assert all(x == 0 for x in sizes[min(ctas, total):])
 
 
 def test_piece_count_formula_matches_ranges():
