@@ -25,9 +25,13 @@ def _newer(src_list, target):
     return any(os.path.getmtime(s) > t for s in src_list)
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, defines=(), lib_path=None):
+    """defines: extra -D macros (tuning experiments build a second library beside the default one)."""
+    global LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    obj_dir = os.path.join(ROOT, "build", "hy3attn")
+    tag = "".join("_" + d.replace("=", "") for d in defines)
+    obj_dir = os.path.join(ROOT, "build", "hy3attn" + tag)
+    lib_out = lib_path or (LIB if not defines else os.path.join(HERE, "libhy3attn%s.so" % tag))
     os.makedirs(obj_dir, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(ROOT, "include", "hy3_attn.h"))
@@ -37,7 +41,7 @@ def build(force=False, verbose=False):
         obj = os.path.join(obj_dir, s.replace(".cu", ".o"))
         objs.append(obj)
         if force or _newer([src] + headers, obj):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            cmd = [nvcc] + NVCC_FLAGS + ["-D" + d for d in defines] + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for s, p in procs:
@@ -47,14 +51,15 @@ def build(force=False, verbose=False):
         failed |= bool(p.returncode)
     if failed:
         raise RuntimeError("nvcc failed")
-    if force or procs or _newer(objs, LIB):
-        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static"]
+    if force or procs or _newer(objs, lib_out):
+        cmd = [nvcc, "-shared", "-o", lib_out] + objs + ["-cudart", "static"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             print(r.stdout + r.stderr)
             raise RuntimeError("link failed")
-    return LIB
+    return lib_out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                defines=tuple(a[2:] for a in sys.argv[1:] if a.startswith("-D"))))

@@ -136,6 +136,11 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->decode_ctas = prop.multiProcessorCount;
     { const char *e = getenv("HY3A_DECODE_CTAS"); if (e && atoi(e) > 0) ctx->decode_ctas = atoi(e); }
+    {   /* ring depth: as many pages as fit in shared memory beside the merge buffers, at most 8 */
+        ctx->decode_stages = hy3a_decode_ring_capacity(ctx->geom.page_bytes, cfg->max_batch);
+        const char *e = getenv("HY3A_DECODE_STAGES");
+        if (e) { int v = atoi(e); if (v < ctx->decode_stages) ctx->decode_stages = v; }
+    }
     CREATE_CUDA(cudaSetDevice(dev));
     CREATE_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
     ctx->own_stream = 1;

@@ -9,7 +9,9 @@
 #include "layout.h"
 
 #define HY3A_MAX_LAYERS 128
-#define HY3A_DECODE_WARPS 8
+#ifndef HY3A_DECODE_WARPS
+#define HY3A_DECODE_WARPS 11
+#endif
 #define HY3A_ERR_WORDS 4
 #define HY3A_RING_SLOTS 16
 
@@ -79,6 +81,7 @@ struct hy3a_ctx {
     unsigned int *h_err;  /* pinned */
     int batch_n;
     int decode_ctas;
+    int decode_stages;    /* pages in the decode kernel's shared-memory ring; < 2 selects the direct-load variant */
 
     hy3a_rope_params rope;
     uint64_t launches;
@@ -96,6 +99,7 @@ int hy3a_launch_export(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint8_t
 int hy3a_launch_fill_random(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint64_t seed);
 int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq, const void *q16, float *out,
                         size_t out_stride);
+int hy3a_decode_ring_capacity(int page_bytes, int max_batch);
 int hy3a_fail(hy3a_ctx *ctx, int code, const char *fmt, ...);
 
 static inline hy3a_cache_view hy3a_view(const hy3a_ctx *c) {

@@ -39,6 +39,11 @@ namespace {
 
 constexpr int kWarps = HY3A_DECODE_WARPS;
 constexpr int kThreads = kWarps * 32;
+constexpr int kFixedO = kWarps * 8 * HY3A_D * 4;
+constexpr int kFixedML = ((kWarps * 8 * 2 * 4) + 127) / 128 * 128;
+constexpr int kFixedQ = 8 * 32 * 16;
+constexpr int kFixed = kFixedO + kFixedML + kFixedQ;   /* bytes of shared memory in front of the page-count prefix */
+constexpr int kSmemMax = 232448 - 1024;                /* opt-in limit per block minus the driver's reserve */
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -77,7 +82,7 @@ __device__ __forceinline__ float2 unpack_h2(unsigned v) {
     return __half22float2(h);
 }
 __device__ __forceinline__ void mma16816(float c[4], const unsigned a[4], unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -131,6 +136,8 @@ struct decode_args {
     unsigned int *counters;
     unsigned int *err;
     int layer;
+    int stages;           /* staged variant: pages in the shared-memory ring (2..8) */
+    int prefix_bytes;     /* staged variant: bytes reserved for the page-count prefix */
 };
 
 struct warp_state {
@@ -139,26 +146,268 @@ struct warp_state {
     float o[16][4];
 };
 
-template <int DT>
-__global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_view cache, hy3a_batch_view batch, decode_args a) {
-    extern __shared__ int s_dyn[];            /* prefix of page counts: [n+1] */
-    __shared__ float s_o[kWarps][8][HY3A_D];  /* per-warp unnormalised outputs */
-    __shared__ float s_ml[kWarps][8][2];
+struct segment {
+    int row, hl, pages, p_begin, p_end, sidx, len, seq;
+    long long seg_u0, seg_u1;
+};
+
+/* Locate the (row, local head) segment that contains unit u and the page range of it that
+ * falls into [u, u_end).                                                                   */
+__device__ __forceinline__ segment locate(const int *s_prefix, const hy3a_batch_view &batch, int n, int G, long long u, long long u_end) {
+    segment sg;
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if ((long long)G * s_prefix[mid] <= u) lo = mid; else hi = mid - 1;
+    }
+    sg.row = lo;
+    sg.pages = s_prefix[lo + 1] - s_prefix[lo];
+    const long long row_u0 = (long long)G * s_prefix[lo];
+    sg.hl = (int)((u - row_u0) / sg.pages);
+    sg.seg_u0 = row_u0 + (long long)sg.hl * sg.pages;
+    sg.seg_u1 = sg.seg_u0 + sg.pages;
+    sg.p_begin = (int)(u - sg.seg_u0);
+    sg.p_end = (int)((sg.seg_u1 < u_end ? sg.seg_u1 : u_end) - sg.seg_u0);
+    sg.sidx = lo * G + sg.hl;
+    sg.len = batch.slot[lo] + 1;
+    sg.seq = batch.seq[lo];
+    return sg;
+}
+
+/* ---- shared-memory / mbarrier / bulk-copy primitives (staged variant) ---------------- */
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint4 lds16(unsigned addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned lds4(unsigned addr) {
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(unsigned bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+__device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void *src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+/* Bounded wait: gives up after ~2^22 polls (far beyond any legitimate wait), records the
+ * failure in the device error word and raises the CTA-wide abort flag; once the flag is up
+ * every later wait returns at once, so all warps keep the same control flow and the kernel
+ * runs to its end (with a meaningless result that the host discards on seeing the error). */
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, unsigned *err, unsigned where) {
+    if (mbar_test(bar, parity)) return true;
+    for (unsigned i = 0; i < (1u << 22); i++) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 255u) == 255u) { if (*abort_flag) return false; __nanosleep(64); }
+    }
+    *abort_flag = 1;
+    if (atomicCAS(err, 0u, 1u) == 0u) err[1] = where;
+    return false;
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
+
+/* One 16-token granule of one warp: loads, S = Q.K^T, online softmax, O += P.V.
+ * SM: operands come from a shared-memory copy of the page (addresses are 32-bit shared
+ * addresses) instead of global memory.                                                  */
+template <int DT, bool SM>
+__device__ __forceinline__ void granule(warp_state &st, unsigned sq, const uint8_t *gpage, unsigned spage, const hy3a_geom &geom,
+                                        const int (&k_off)[2][4], const int (&v_off)[8], const int (&sc_off)[2], int gi, int tig, int valid,
+                                        float pscale) {
+    /* page-relative byte offsets of granule gi (16 tokens = 16 K rows = 8 V pair-rows) */
+    const int gk = gi * 16 * geom.k_row, gv = geom.v_off + gi * (DT == 0 ? 16 : 8) * geom.v_prow, gs = gi * 32;
+    gpage += 0;
+    constexpr int NK = DT == 0 ? 4 : (DT == 1 ? 2 : 1);
+    constexpr int NV = DT == 0 ? 8 : (DT == 1 ? 4 : 2);
+    uint4 kr[2][NK];
+#pragma unroll
+    for (int nb = 0; nb < 2; nb++) {
+#pragma unroll
+        for (int i = 0; i < NK; i++) kr[nb][i] = SM ? lds16(spage + gk + k_off[nb][i]) : ld16(gpage + gk + k_off[nb][i]);
+    }
+    unsigned ksw[2] = {0, 0}, vsw[2] = {0, 0};
+    if (DT != 0) {
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++) {
+            ksw[nb] = SM ? lds4(spage + geom.ks_off + gs + sc_off[nb]) : ld4(gpage + geom.ks_off + gs + sc_off[nb]);
+            vsw[nb] = SM ? lds4(spage + geom.vs_off + gs + sc_off[nb]) : ld4(gpage + geom.vs_off + gs + sc_off[nb]);
+        }
+    }
+    uint4 vr[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) vr[i] = SM ? lds16(spage + gv + v_off[i]) : ld16(gpage + gv + v_off[i]);
+    /* Q operand fragments of this thread for the 8 k-steps, pre-packed in shared memory */
+    unsigned qa[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++) { uint4 t = lds16(sq + j * 512); qa[j][0] = t.x; qa[j][1] = t.y; qa[j][2] = t.z; qa[j][3] = t.w; }
+
+    /* ---- S = Q.K^T for the two 8-token n-blocks; even and odd k-steps accumulate separately so
+     * that four independent MMA chains are in flight instead of two                              */
+    float sc[2][4], sd[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 2; nb++) { sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f; sd[nb][0] = sd[nb][1] = sd[nb][2] = sd[nb][3] = 0.f; }
+    if (DT == 1) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+#pragma unroll
+            for (int r = 0; r < 4; r += 2) {
+#pragma unroll
+                for (int nb = 0; nb < 2; nb++) {
+                    const unsigned w0 = (r == 0 ? kr[nb][i].x : kr[nb][i].z) ^ 0x80808080u;
+                    const unsigned w1 = (r == 0 ? kr[nb][i].y : kr[nb][i].w) ^ 0x80808080u;
+                    mma16816(sc[nb], qa[4 * i + r], cvt_i8(w0, 0x4140u), cvt_i8(w0, 0x4342u));
+                    mma16816(sd[nb], qa[4 * i + r + 1], cvt_i8(w1, 0x4140u), cvt_i8(w1, 0x4342u));
+                }
+            }
+        }
+    } else if (DT == 2) {
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++) {
+                const unsigned w = (r == 0 ? kr[nb][0].x : (r == 1 ? kr[nb][0].y : (r == 2 ? kr[nb][0].z : kr[nb][0].w)));
+                const unsigned xs = w ^ 0x88888888u, xh = xs >> 8;
+                mma16816(sc[nb], qa[2 * r], cvt_i4_lo(xs), cvt_i4_hi(xs));
+                mma16816(sd[nb], qa[2 * r + 1], cvt_i4_lo(xh), cvt_i4_hi(xh));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NK; i++) {
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++) {
+                mma16816(sc[nb], qa[2 * i], kr[nb][i].x, kr[nb][i].y);
+                mma16816(sd[nb], qa[2 * i + 1], kr[nb][i].z, kr[nb][i].w);
+            }
+        }
+    }
+#pragma unroll
+    for (int nb = 0; nb < 2; nb++) { sc[nb][0] += sd[nb][0]; sc[nb][1] += sd[nb][1]; sc[nb][2] += sd[nb][2]; sc[nb][3] += sd[nb][3]; }
+    /* ---- scores of head g for tokens 16w + 8nb + 2tig + e */
+    float s[2][2], vs[2][2];
+#pragma unroll
+    for (int nb = 0; nb < 2; nb++) {
+        float2 kf = make_float2(1.f, 1.f), vf = make_float2(1.f, 1.f);
+        if (DT != 0) { kf = unpack_h2(ksw[nb]); vf = unpack_h2(vsw[nb]); }
+        int t0 = 16 * gi + 8 * nb + 2 * tig;
+        float r0 = sc[nb][0] + sc[nb][2], r1 = sc[nb][1] + sc[nb][3];
+        s[nb][0] = (t0 < valid) ? r0 * kf.x : -INFINITY;
+        s[nb][1] = (t0 + 1 < valid) ? r1 * kf.y : -INFINITY;
+        vs[nb][0] = (t0 < valid) ? vf.x * pscale : 0.f;
+        vs[nb][1] = (t0 + 1 < valid) ? vf.y * pscale : 0.f;
+    }
+    float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(st.m, mx); /* finite: token 16w of this granule is valid */
+    if (__any_sync(0xffffffffu, m_new > st.m)) {
+        const float alpha = ex2(st.m - m_new); /* 0 on the first granule (m = -inf) */
+        st.l *= alpha;
+#pragma unroll
+        for (int jn = 0; jn < 16; jn++) { st.o[jn][0] *= alpha; st.o[jn][1] *= alpha; st.o[jn][2] *= alpha; st.o[jn][3] *= alpha; }
+        st.m = m_new;
+    }
+    unsigned pa[4];
+    {
+        float w[2][2];
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                float pe = ex2(s[nb][e] - st.m); /* -inf -> 0 */
+                st.l += pe;
+                w[nb][e] = pe * vs[nb][e];
+            }
+        }
+        pa[0] = pack_h2(w[0][0], w[0][1]);
+        pa[2] = pack_h2(w[1][0], w[1][1]);
+        float2 h0 = unpack_h2(pa[0]), h1 = unpack_h2(pa[2]);
+        pa[1] = pack_h2(w[0][0] - h0.x, w[0][1] - h0.y);
+        pa[3] = pack_h2(w[1][0] - h1.x, w[1][1] - h1.y);
+    }
+    /* ---- O += P.V over 16 n-blocks of 8 output dims */
+    if (DT == 1) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            unsigned a4[4] = {vr[half].x, vr[half].y, vr[half].z, vr[half].w};
+            unsigned b4[4] = {vr[2 + half].x, vr[2 + half].y, vr[2 + half].z, vr[2 + half].w};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                unsigned xa = a4[k] ^ 0x80808080u, xb = b4[k] ^ 0x80808080u;
+                mma16816(st.o[8 * half + 2 * k], pa, cvt_i8(xa, 0x4240u), cvt_i8(xb, 0x4240u));
+                mma16816(st.o[8 * half + 2 * k + 1], pa, cvt_i8(xa, 0x4341u), cvt_i8(xb, 0x4341u));
+            }
+        }
+    } else if (DT == 2) {
+        unsigned a4[4] = {vr[0].x, vr[0].y, vr[0].z, vr[0].w};
+        unsigned b4[4] = {vr[1].x, vr[1].y, vr[1].z, vr[1].w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            unsigned xa = a4[k] ^ 0x88888888u, xb = b4[k] ^ 0x88888888u, xah = xa >> 8, xbh = xb >> 8;
+            mma16816(st.o[4 * k + 0], pa, cvt_i4_lo(xa), cvt_i4_lo(xb));
+            mma16816(st.o[4 * k + 1], pa, cvt_i4_hi(xa), cvt_i4_hi(xb));
+            mma16816(st.o[4 * k + 2], pa, cvt_i4_lo(xah), cvt_i4_lo(xbh));
+            mma16816(st.o[4 * k + 3], pa, cvt_i4_hi(xah), cvt_i4_hi(xbh));
+        }
+    } else {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            /* vr[2t + half]: token t (A,B = b0 pair; C,D = b1 pair), chunk g + 8*half */
+            unsigned tA[4] = {vr[0 + half].x, vr[0 + half].y, vr[0 + half].z, vr[0 + half].w};
+            unsigned tB[4] = {vr[2 + half].x, vr[2 + half].y, vr[2 + half].z, vr[2 + half].w};
+            unsigned tC[4] = {vr[4 + half].x, vr[4 + half].y, vr[4 + half].z, vr[4 + half].w};
+            unsigned tD[4] = {vr[6 + half].x, vr[6 + half].y, vr[6 + half].z, vr[6 + half].w};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                mma16816(st.o[8 * half + 2 * k], pa, prmt(tA[k], tB[k], 0x5410u), prmt(tC[k], tD[k], 0x5410u));
+                mma16816(st.o[8 * half + 2 * k + 1], pa, prmt(tA[k], tB[k], 0x7632u), prmt(tC[k], tD[k], 0x7632u));
+            }
+        }
+    }
+}
+
+/* DIRECT variant: 8 warps, operands fetched straight from global memory with 128-bit loads.
+ * STAGED variant: 8 consumer warps + 1 producer warp; the producer streams whole pages into a
+ * shared-memory ring with bulk asynchronous copies (cp.async.bulk + mbarrier transaction
+ * counts), consumers read their fragments from the ring.  Same arithmetic, same results.  */
+template <int DT, bool STAGED>
+__global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_kernel(hy3a_cache_view cache, hy3a_batch_view batch, decode_args a) {
+    /* dynamic shared memory: [s_o | s_ml | s_q | page-count prefix | full[8] empty[8] | ring of pages] */
+    extern __shared__ __align__(128) uint8_t s_dyn[];
+    float (*s_o)[8][HY3A_D] = reinterpret_cast<float (*)[8][HY3A_D]>(s_dyn);                       /* per-warp unnormalised outputs */
+    float (*s_ml)[8][2] = reinterpret_cast<float (*)[8][2]>(s_dyn + kFixedO);                      /* per-warp {m, l} */
+    uint4 (*s_q)[32] = reinterpret_cast<uint4 (*)[32]>(s_dyn + kFixedO + kFixedML);                /* Q fragments: [k-step][lane] */
     __shared__ int s_flag;
+    __shared__ int s_abort;
 
     const hy3a_geom geom = hy3a_make_geom(DT);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tig = lane & 3;
     const int n = batch.n, G = cache.kv_heads;
     const int cta = blockIdx.x;
-    int *s_prefix = s_dyn;
+    int *s_prefix = reinterpret_cast<int *>(s_dyn + kFixed);
+    const unsigned bar_base = smem_u32(s_dyn + kFixed + a.prefix_bytes);
+    const unsigned ring_base = bar_base + 128;
 
     /* ---- schedule: prefix of pages per row */
-    for (int i = tid; i < n; i += kThreads) {
+    for (int i = tid; i < n; i += blockDim.x) {
         int len = batch.slot[i] + 1;
         s_prefix[i + 1] = len > 0 ? (len + HY3A_PT - 1) / HY3A_PT : 0;
     }
-    if (tid == 0) s_prefix[0] = 0;
+    if (tid == 0) {
+        s_prefix[0] = 0;
+        s_abort = 0;
+        if (STAGED) {
+            for (int i = 0; i < a.stages; i++) { mbar_init(bar_base + 8 * i, 1); mbar_init(bar_base + 64 + 8 * i, 256); }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
     __syncthreads();
     if (warp == 0) {
         int carry = 0;
@@ -179,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
     /* rows with no keys on this rank: zero output / empty partial (hy3_gpu.cu:197-199) */
     for (int i = cta; i < n; i += gridDim.x) {
         if (s_prefix[i + 1] != s_prefix[i]) continue;
-        for (int e = tid; e < G * 8 * HY3A_D; e += kThreads) {
+        for (int e = tid; e < G * 8 * HY3A_D; e += blockDim.x) {
             int hq = e / HY3A_D, d = e % HY3A_D;
             if (a.user_partials) {
                 float *p = a.user_partials + ((size_t)i * G * 8 + hq) * HY3A_PARTIAL_FLOATS;
@@ -198,20 +447,53 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
     if (cta >= C) return;
     const long long u_begin = (long long)cta * U / C, u_end = (long long)(cta + 1) * U / C;
 
-    /* per-thread page-relative offsets (loop invariant) */
-    int k_off[2][4];   /* [n-block][chunk] */
+    if (STAGED && warp == kWarps) {
+        /* ================= producer warp: one lane streams the CTA's pages into the ring */
+        if (lane == 0) {
+            unsigned it = 0;
+            bool ok = true;
+            for (long long u = u_begin; u < u_end && ok;) {
+                segment sg = locate(s_prefix, batch, n, G, u, u_end);
+                const int *bt = cache.block_table + (size_t)sg.seq * cache.max_blocks_per_seq;
+                int block_next = bt[sg.p_begin];
+                for (int p = sg.p_begin; p < sg.p_end && ok; p++, it++) {
+                    const unsigned stage = it % (unsigned)a.stages, phase = (it / (unsigned)a.stages) & 1u;
+                    const int block = block_next;
+                    if (p + 1 < sg.p_end) block_next = bt[p + 1];   /* in flight while we wait for the stage */
+                    ok = mbar_wait(bar_base + 64 + 8 * stage, phase ^ 1u, &s_abort, a.err, 1u);
+                    if (!ok) break;
+                    const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, sg.hl) * (size_t)cache.page_bytes;
+                    mbar_expect_tx(bar_base + 8 * stage, (unsigned)geom.page_bytes);
+                    bulk_g2s(ring_base + stage * (unsigned)geom.page_bytes, page, (unsigned)geom.page_bytes, bar_base + 8 * stage);
+                }
+                u = sg.seg_u0 + sg.p_end;
+            }
+            if (!ok) {
+                /* gave up: let the copies already issued land before the CTA's shared memory goes away */
+                const unsigned first = it > (unsigned)a.stages ? it - (unsigned)a.stages : 0u;
+                for (unsigned j = first; j < it; j++) {
+                    const unsigned stage = j % (unsigned)a.stages, phase = (j / (unsigned)a.stages) & 1u;
+                    for (unsigned spin = 0; spin < (1u << 20) && !mbar_test(bar_base + 8 * stage, phase); spin++) __nanosleep(64);
+                }
+            }
+        }
+        return;
+    }
+
+    /* ================= consumer warps */
+    int k_off[2][4];   /* [n-block][chunk], page-relative, loop invariant */
     int v_off[8];
     int sc_off[2];
 #pragma unroll
     for (int nb = 0; nb < 2; nb++) {
-        int tok = 16 * warp + 8 * nb + g;
+        int tok = 8 * nb + g;
         if (DT == 1) { k_off[nb][0] = hy3a_k_chunk_off<1>(tok, tig); k_off[nb][1] = hy3a_k_chunk_off<1>(tok, tig + 4); k_off[nb][2] = k_off[nb][3] = 0; }
         else if (DT == 2) { k_off[nb][0] = hy3a_k_chunk_off<2>(tok, tig); k_off[nb][1] = k_off[nb][2] = k_off[nb][3] = 0; }
         else { for (int i = 0; i < 4; i++) k_off[nb][i] = hy3a_k_chunk_off<0>(tok, tig + 4 * i); }
-        sc_off[nb] = 2 * (16 * warp + 8 * nb + 2 * tig);
+        sc_off[nb] = 2 * (8 * nb + 2 * tig);
     }
     {
-        int pr0 = 8 * warp + tig, pr1 = pr0 + 4;
+        int pr0 = tig, pr1 = pr0 + 4;
         if (DT == 1) {
             v_off[0] = hy3a_v_chunk_off<1>(pr0, g); v_off[1] = hy3a_v_chunk_off<1>(pr0, g + 8);
             v_off[2] = hy3a_v_chunk_off<1>(pr1, g); v_off[3] = hy3a_v_chunk_off<1>(pr1, g + 8);
@@ -220,7 +502,7 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
             v_off[0] = hy3a_v_chunk_off<2>(pr0, g); v_off[1] = hy3a_v_chunk_off<2>(pr1, g);
             for (int i = 2; i < 8; i++) v_off[i] = 0;
         } else {
-            int tA = 16 * warp + 2 * tig;
+            int tA = 2 * tig;
             for (int t = 0; t < 4; t++) {
                 int tok = tA + (t & 1) + 8 * (t >> 1);
                 v_off[2 * t] = hy3a_v16_chunk_off(tok, g);
@@ -229,44 +511,28 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
         }
     }
 
+    unsigned it = 0; /* pages consumed by this CTA so far (ring position) */
     long long u = u_begin;
     while (u < u_end) {
-        /* ---- locate the segment (row i, local head hl) that contains unit u */
-        int lo = 0, hi = n - 1;
-        while (lo < hi) {
-            int mid = (lo + hi + 1) >> 1;
-            if ((long long)G * s_prefix[mid] <= u) lo = mid; else hi = mid - 1;
-        }
-        const int row = lo;
-        const int pages = s_prefix[row + 1] - s_prefix[row];
-        const long long row_u0 = (long long)G * s_prefix[row];
-        const int hl = (int)((u - row_u0) / pages);
-        const long long seg_u0 = row_u0 + (long long)hl * pages, seg_u1 = seg_u0 + pages;
-        const int p_begin = (int)(u - seg_u0);
-        const int p_end = (int)((seg_u1 < u_end ? seg_u1 : u_end) - seg_u0);
-        const int sidx = row * G + hl;
-        const int len = batch.slot[row] + 1;
-        const int seq = batch.seq[row];
+        const segment sg = locate(s_prefix, batch, n, G, u, u_end);
+        const int row = sg.row, hl = sg.hl, sidx = sg.sidx;
 
         /* ---- Q operand fragments: fp16 value in rows 0-7, fp16 residual in rows 8-15.
-         * softmax scale 1/sqrt(128) (hy3_gpu.cu:193) and log2(e) are folded into Q.     */
-        unsigned qa[8][4];
-        {
+         * softmax scale 1/sqrt(128) (hy3_gpu.cu:193) and log2(e) are folded into Q.  Thread t < 256
+         * packs the entry of k-step t/32 for lane t%32; every warp then reads its lanes' entries. */
+        if (tid < 256) {
+            const int j = tid >> 5;
             const float *qh = a.q + (size_t)row * a.q_stride + (size_t)((cache.kv_head_begin + hl) * 8 + g) * HY3A_D;
             const float qs = 0.08838834764831845f * kLog2e;
+            float x[4], hi4[4], lo4[4];
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                float x[4], hi4[4], lo4[4];
+            for (int s = 0; s < 4; s++) x[s] = qh[kdim<DT>(j, tig, s)] * qs;
 #pragma unroll
-                for (int s = 0; s < 4; s++) x[s] = qh[kdim<DT>(j, tig, s)] * qs;
-#pragma unroll
-                for (int s = 0; s < 4; s++) { hi4[s] = __half2float(__float2half_rn(x[s])); lo4[s] = x[s] - hi4[s]; }
-                qa[j][0] = pack_h2(hi4[0], hi4[1]);
-                qa[j][1] = pack_h2(lo4[0], lo4[1]);
-                qa[j][2] = pack_h2(hi4[2], hi4[3]);
-                qa[j][3] = pack_h2(lo4[2], lo4[3]);
-            }
+            for (int s = 0; s < 4; s++) { hi4[s] = __half2float(__float2half_rn(x[s])); lo4[s] = x[s] - hi4[s]; }
+            s_q[j][lane] = make_uint4(pack_h2(hi4[0], hi4[1]), pack_h2(lo4[0], lo4[1]), pack_h2(hi4[2], hi4[3]), pack_h2(lo4[2], lo4[3]));
         }
+        consumer_sync();
+        const unsigned sq = smem_u32(&s_q[0][lane]);
         /* P scale: w = p * vscale * 2^E with vs_max * 2^E <= 2^14, so fp16 P never
          * overflows and its subnormal floor sits 2^-38 below the row maximum.          */
         float pscale;
@@ -289,142 +555,28 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
 #pragma unroll
         for (int jn = 0; jn < 16; jn++) { st.o[jn][0] = st.o[jn][1] = st.o[jn][2] = st.o[jn][3] = 0.f; }
 
-        for (int p = p_begin; p < p_end; p++) {
-            const int valid = min(HY3A_PT, len - p * HY3A_PT);
-            if (16 * warp >= valid) continue; /* warp-uniform */
-            const int block = cache.block_table[(size_t)seq * cache.max_blocks_per_seq + p];
-            const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, hl) * (size_t)cache.page_bytes;
-            const uint8_t *vbase = page + geom.v_off;
-
-            /* ---- issue all loads of the granule */
-            uint4 kr[2][DT == 0 ? 4 : (DT == 1 ? 2 : 1)];
-#pragma unroll
-            for (int nb = 0; nb < 2; nb++) {
-#pragma unroll
-                for (int i = 0; i < (DT == 0 ? 4 : (DT == 1 ? 2 : 1)); i++) kr[nb][i] = ld16(page + k_off[nb][i]);
-            }
-            unsigned ksw[2] = {0, 0}, vsw[2] = {0, 0};
-            if (DT != 0) {
-#pragma unroll
-                for (int nb = 0; nb < 2; nb++) { ksw[nb] = ld4(page + geom.ks_off + sc_off[nb]); vsw[nb] = ld4(page + geom.vs_off + sc_off[nb]); }
-            }
-            uint4 vr[DT == 0 ? 8 : (DT == 1 ? 4 : 2)];
-#pragma unroll
-            for (int i = 0; i < (DT == 0 ? 8 : (DT == 1 ? 4 : 2)); i++) vr[i] = ld16(vbase + v_off[i]);
-
-            /* ---- S = Q.K^T for the two 8-token n-blocks */
-            float sc[2][4];
-#pragma unroll
-            for (int nb = 0; nb < 2; nb++) {
-                sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
-                if (DT == 1) {
-#pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        unsigned w4[4] = {kr[nb][i].x, kr[nb][i].y, kr[nb][i].z, kr[nb][i].w};
-#pragma unroll
-                        for (int r = 0; r < 4; r++) {
-                            unsigned xs = w4[r] ^ 0x80808080u;
-                            mma16816(sc[nb], qa[4 * i + r], cvt_i8(xs, 0x4140u), cvt_i8(xs, 0x4342u));
-                        }
-                    }
-                } else if (DT == 2) {
-                    unsigned w4[4] = {kr[nb][0].x, kr[nb][0].y, kr[nb][0].z, kr[nb][0].w};
-#pragma unroll
-                    for (int r = 0; r < 4; r++) {
-                        unsigned xs = w4[r] ^ 0x88888888u, xh = xs >> 8;
-                        mma16816(sc[nb], qa[2 * r], cvt_i4_lo(xs), cvt_i4_hi(xs));
-                        mma16816(sc[nb], qa[2 * r + 1], cvt_i4_lo(xh), cvt_i4_hi(xh));
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        mma16816(sc[nb], qa[2 * i], kr[nb][i].x, kr[nb][i].y);
-                        mma16816(sc[nb], qa[2 * i + 1], kr[nb][i].z, kr[nb][i].w);
-                    }
-                }
-            }
-            /* ---- scores of head g for tokens 16w + 8nb + 2tig + e */
-            float s[2][2], vs[2][2];
-#pragma unroll
-            for (int nb = 0; nb < 2; nb++) {
-                float2 kf = make_float2(1.f, 1.f), vf = make_float2(1.f, 1.f);
-                if (DT != 0) { kf = unpack_h2(ksw[nb]); vf = unpack_h2(vsw[nb]); }
-                int t0 = 16 * warp + 8 * nb + 2 * tig;
-                float r0 = sc[nb][0] + sc[nb][2], r1 = sc[nb][1] + sc[nb][3];
-                s[nb][0] = (t0 < valid) ? r0 * kf.x : -INFINITY;
-                s[nb][1] = (t0 + 1 < valid) ? r1 * kf.y : -INFINITY;
-                vs[nb][0] = (t0 < valid) ? vf.x * pscale : 0.f;
-                vs[nb][1] = (t0 + 1 < valid) ? vf.y * pscale : 0.f;
-            }
-            float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(st.m, mx); /* finite: token 16w of this granule is valid */
-            if (__any_sync(0xffffffffu, m_new > st.m)) {
-                const float alpha = ex2(st.m - m_new); /* 0 on the first granule (m = -inf) */
-                st.l *= alpha;
-#pragma unroll
-                for (int jn = 0; jn < 16; jn++) { st.o[jn][0] *= alpha; st.o[jn][1] *= alpha; st.o[jn][2] *= alpha; st.o[jn][3] *= alpha; }
-                st.m = m_new;
-            }
-            unsigned pa[4];
-            {
-                float w[2][2];
-#pragma unroll
-                for (int nb = 0; nb < 2; nb++) {
-#pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        float pe = ex2(s[nb][e] - st.m); /* -inf -> 0 */
-                        st.l += pe;
-                        w[nb][e] = pe * vs[nb][e];
-                    }
-                }
-                pa[0] = pack_h2(w[0][0], w[0][1]);
-                pa[2] = pack_h2(w[1][0], w[1][1]);
-                float2 h0 = unpack_h2(pa[0]), h1 = unpack_h2(pa[2]);
-                pa[1] = pack_h2(w[0][0] - h0.x, w[0][1] - h0.y);
-                pa[3] = pack_h2(w[1][0] - h1.x, w[1][1] - h1.y);
-            }
-            /* ---- O += P.V over 16 n-blocks of 8 output dims */
-            if (DT == 1) {
-#pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    unsigned a4[4] = {vr[half].x, vr[half].y, vr[half].z, vr[half].w};
-                    unsigned b4[4] = {vr[2 + half].x, vr[2 + half].y, vr[2 + half].z, vr[2 + half].w};
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        unsigned xa = a4[k] ^ 0x80808080u, xb = b4[k] ^ 0x80808080u;
-                        mma16816(st.o[8 * half + 2 * k], pa, cvt_i8(xa, 0x4240u), cvt_i8(xb, 0x4240u));
-                        mma16816(st.o[8 * half + 2 * k + 1], pa, cvt_i8(xa, 0x4341u), cvt_i8(xb, 0x4341u));
-                    }
-                }
-            } else if (DT == 2) {
-                unsigned a4[4] = {vr[0].x, vr[0].y, vr[0].z, vr[0].w};
-                unsigned b4[4] = {vr[1].x, vr[1].y, vr[1].z, vr[1].w};
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    unsigned xa = a4[k] ^ 0x88888888u, xb = b4[k] ^ 0x88888888u, xah = xa >> 8, xbh = xb >> 8;
-                    mma16816(st.o[4 * k + 0], pa, cvt_i4_lo(xa), cvt_i4_lo(xb));
-                    mma16816(st.o[4 * k + 1], pa, cvt_i4_hi(xa), cvt_i4_hi(xb));
-                    mma16816(st.o[4 * k + 2], pa, cvt_i4_lo(xah), cvt_i4_lo(xbh));
-                    mma16816(st.o[4 * k + 3], pa, cvt_i4_hi(xah), cvt_i4_hi(xbh));
-                }
+        /* granule slot x = 8*(ring position of the page) + granule-in-page; warp w takes slots
+         * x = w (mod kWarps), so any number of consumer warps shares the 8 granules of a page and
+         * each page is released by exactly 8 warps (one arrival per thread per slot).            */
+        const unsigned it_end = it + (unsigned)(sg.p_end - sg.p_begin);
+        for (unsigned x = it * 8u + ((unsigned)warp + kWarps - (it * 8u) % kWarps) % kWarps; x < it_end * 8u; x += kWarps) {
+            const unsigned pit = x >> 3;
+            const int gi = (int)(x & 7u), p = sg.p_begin + (int)(pit - it);
+            const int valid = min(HY3A_PT, sg.len - p * HY3A_PT);
+            if (STAGED) {
+                const unsigned stage = pit % (unsigned)a.stages, phase = (pit / (unsigned)a.stages) & 1u;
+                mbar_wait(bar_base + 8 * stage, phase, &s_abort, a.err, 2u);
+                if (16 * gi < valid)
+                    granule<DT, true>(st, sq, nullptr, ring_base + stage * (unsigned)geom.page_bytes, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
+                mbar_arrive(bar_base + 64 + 8 * stage); /* every thread of the 8 warps that share a page releases it */
             } else {
-#pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    /* vr[2t + half]: token t (A,B = b0 pair; C,D = b1 pair), chunk g + 8*half */
-                    unsigned tA[4] = {vr[0 + half].x, vr[0 + half].y, vr[0 + half].z, vr[0 + half].w};
-                    unsigned tB[4] = {vr[2 + half].x, vr[2 + half].y, vr[2 + half].z, vr[2 + half].w};
-                    unsigned tC[4] = {vr[4 + half].x, vr[4 + half].y, vr[4 + half].z, vr[4 + half].w};
-                    unsigned tD[4] = {vr[6 + half].x, vr[6 + half].y, vr[6 + half].z, vr[6 + half].w};
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        mma16816(st.o[8 * half + 2 * k], pa, prmt(tA[k], tB[k], 0x5410u), prmt(tC[k], tD[k], 0x5410u));
-                        mma16816(st.o[8 * half + 2 * k + 1], pa, prmt(tA[k], tB[k], 0x7632u), prmt(tC[k], tD[k], 0x7632u));
-                    }
-                }
+                if (16 * gi >= valid) continue; /* warp-uniform */
+                const int block = cache.block_table[(size_t)sg.seq * cache.max_blocks_per_seq + p];
+                const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, hl) * (size_t)cache.page_bytes;
+                granule<DT, false>(st, sq, page, 0u, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
             }
         }
+        it = it_end;
 
         /* ---- fold the 8 warps of this CTA (shared memory) */
         {
@@ -439,8 +591,9 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
                 s_o[warp][g][vdim<DT>(jn, 2 * tig + 1)] = (st.o[jn][1] + st.o[jn][3]) * inv_ps;
             }
         }
-        __syncthreads();
-        const int h = tid >> 5, d4 = (tid & 31) * 4; /* thread -> (head, 4 dims) */
+        consumer_sync();
+        const bool red = tid < 256;                            /* the first 8 warps do the reductions */
+        const int h = (tid >> 5) & 7, d4 = (tid & 31) * 4;    /* thread -> (head, 4 dims) */
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kWarps; w++) M = fmaxf(M, s_ml[w][h][0]);
@@ -454,41 +607,52 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
             float4 o4 = *reinterpret_cast<const float4 *>(&s_o[w][h][d4]);
             acc[0] += o4.x * f; acc[1] += o4.y * f; acc[2] += o4.z * f; acc[3] += o4.w * f;
         }
-        __syncthreads(); /* s_o / s_ml free for the next segment */
+        consumer_sync(); /* s_o / s_ml free for the next segment */
 
         /* ---- how many CTAs share this segment? */
-        const int c_first = (int)(((seg_u0 + 1) * C + U - 1) / U) - 1;
-        const int c_last = (int)((seg_u1 * C + U - 1) / U) - 1;
+        const int c_first = (int)(((sg.seg_u0 + 1) * C + U - 1) / U) - 1;
+        const int c_last = (int)((sg.seg_u1 * C + U - 1) / U) - 1;
         const int npieces = c_last - c_first + 1;
         const size_t head_q = (size_t)(cache.kv_head_begin + hl) * 8 + h; /* global query head */
+        u = sg.seg_u0 + sg.p_end;
 
         if (npieces > 1) {
             float *rec = a.scratch + ((size_t)(cta + sidx) * 8 + h) * HY3A_PARTIAL_FLOATS;
-            if (d4 == 0) { rec[0] = M; rec[1] = L; }
-            rec[2 + d4] = acc[0]; rec[3 + d4] = acc[1]; rec[4 + d4] = acc[2]; rec[5 + d4] = acc[3];
+            if (red) {
+                if (d4 == 0) { rec[0] = M; rec[1] = L; }
+                rec[2 + d4] = acc[0]; rec[3 + d4] = acc[1]; rec[4 + d4] = acc[2]; rec[5 + d4] = acc[3];
+            }
             __threadfence();
-            __syncthreads();
+            consumer_sync();
             if (tid == 0) {
                 unsigned old = atomicAdd(a.counters + sidx, 1u);
                 s_flag = (old == (unsigned)(npieces - 1));
             }
-            __syncthreads();
-            if (!s_flag) { u = seg_u0 + p_end; continue; }
+            consumer_sync();
+            if (!s_flag || !red) continue;
             __threadfence();
-            /* last arrival: fold all pieces in CTA order (hy3_gpu.cu:233-247 rule) */
-            M = -INFINITY; L = 0.f; acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            /* last arrival: fold all pieces (hy3_gpu.cu:233-247 rule).  Two passes so that the
+             * loads of different pieces are independent and overlap: first the maxima, then the
+             * rescaled sums.  __ldcg reads L2, where the other CTAs' records are after their fence. */
+            M = -INFINITY;
             for (int c = c_first; c <= c_last; c++) {
-                const volatile float *pr = a.scratch + ((size_t)(c + sidx) * 8 + h) * HY3A_PARTIAL_FLOATS;
-                float pm = pr[0], pl = pr[1];
-                if (!(pl > 0.f)) continue;
-                float nm = fmaxf(M, pm), os = ex2(M - nm), rs = ex2(pm - nm);
-                L = L * os + pl * rs;
-                acc[0] = acc[0] * os + pr[2 + d4] * rs; acc[1] = acc[1] * os + pr[3 + d4] * rs;
-                acc[2] = acc[2] * os + pr[4 + d4] * rs; acc[3] = acc[3] * os + pr[5 + d4] * rs;
-                M = nm;
+                const float *pr = a.scratch + ((size_t)(c + sidx) * 8 + h) * HY3A_PARTIAL_FLOATS;
+                const float pm = __ldcg(pr), pl = __ldcg(pr + 1);
+                M = fmaxf(M, pl > 0.f ? pm : -INFINITY);
+            }
+            L = 0.f; acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+#pragma unroll 4
+            for (int c = c_first; c <= c_last; c++) {
+                const float *pr = a.scratch + ((size_t)(c + sidx) * 8 + h) * HY3A_PARTIAL_FLOATS;
+                const float pm = __ldcg(pr), pl = __ldcg(pr + 1);
+                const float2 a01 = __ldcg(reinterpret_cast<const float2 *>(pr + 2 + d4)), a23 = __ldcg(reinterpret_cast<const float2 *>(pr + 4 + d4));
+                const float rs = pl > 0.f ? ex2(pm - M) : 0.f;
+                L += pl * rs;
+                acc[0] += a01.x * rs; acc[1] += a01.y * rs; acc[2] += a23.x * rs; acc[3] += a23.y * rs;
             }
             if (tid == 0) a.counters[sidx] = 0u; /* self-reset for the next launch */
         }
+        if (!red) continue;
         if (a.user_partials) {
             float *rec = a.user_partials + ((size_t)row * G * 8 + (size_t)hl * 8 + h) * HY3A_PARTIAL_FLOATS;
             if (d4 == 0) { rec[0] = M * kLn2; rec[1] = L; } /* m in natural-log units like the reference record */
@@ -498,7 +662,6 @@ __global__ void __launch_bounds__(kThreads, 1) hy3a_decode_kernel(hy3a_cache_vie
             float4 o4 = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
             *reinterpret_cast<float4 *>(a.out + (size_t)row * a.out_stride + head_q * HY3A_D + d4) = o4;
         }
-        u = seg_u0 + p_end;
     }
 }
 
@@ -523,21 +686,55 @@ __global__ void hy3a_merge_kernel(const float *partials, int n_parts, int n_rows
 
 } /* namespace */
 
+template <int DT>
+static cudaError_t launch_decode_dt(hy3a_ctx *ctx, const hy3a_cache_view &cv, const hy3a_batch_view &bv, decode_args &a) {
+    const size_t prefix = ((size_t)(ctx->batch_n + 1) * sizeof(int) + 127) & ~(size_t)127;
+    dim3 grid(ctx->decode_ctas);
+    static bool attr_set[3][2] = {{false, false}, {false, false}, {false, false}};
+    a.prefix_bytes = (int)prefix;
+    if (ctx->decode_stages >= 2) {
+        a.stages = ctx->decode_stages;
+        const size_t smem = kFixed + prefix + 128 + (size_t)a.stages * ctx->geom.page_bytes;
+        if (!attr_set[DT][1]) {
+            cudaError_t e = cudaFuncSetAttribute(hy3a_decode_kernel<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+            if (e != cudaSuccess) return e;
+            attr_set[DT][1] = true;
+        }
+        hy3a_decode_kernel<DT, true><<<grid, kThreads + 32, smem, ctx->stream>>>(cv, bv, a);
+    } else {
+        a.stages = 0;
+        if (!attr_set[DT][0]) {
+            cudaError_t e = cudaFuncSetAttribute(hy3a_decode_kernel<DT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+            if (e != cudaSuccess) return e;
+            attr_set[DT][0] = true;
+        }
+        hy3a_decode_kernel<DT, false><<<grid, kThreads, kFixed + prefix + 128, ctx->stream>>>(cv, bv, a);
+    }
+    return cudaGetLastError();
+}
+
+/* Pages that fit in the ring for a given page size and batch capacity. */
+int hy3a_decode_ring_capacity(int page_bytes, int max_batch) {
+    const size_t prefix = ((size_t)(max_batch + 1) * sizeof(int) + 127) & ~(size_t)127;
+    long room = (long)kSmemMax - (long)kFixed - (long)prefix - 128;
+    int s = room > 0 ? (int)(room / page_bytes) : 0;
+    return s > 8 ? 8 : s;
+}
+
 int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride, float *partials) {
     decode_args a;
     a.q = q; a.q_stride = q_stride; a.out = out; a.out_stride = out_stride; a.user_partials = partials;
     a.scratch = ctx->d_partials; a.counters = ctx->d_counters; a.err = ctx->d_err; a.layer = layer;
     hy3a_cache_view cv = hy3a_view(ctx);
     hy3a_batch_view bv = hy3a_bview(ctx);
-    size_t smem = (size_t)(ctx->batch_n + 1) * sizeof(int);
-    dim3 grid(ctx->decode_ctas), block(kThreads);
+    cudaError_t e;
     switch (ctx->cfg.kv_dtype) {
-        case 0: hy3a_decode_kernel<0><<<grid, block, smem, ctx->stream>>>(cv, bv, a); break;
-        case 1: hy3a_decode_kernel<1><<<grid, block, smem, ctx->stream>>>(cv, bv, a); break;
-        default: hy3a_decode_kernel<2><<<grid, block, smem, ctx->stream>>>(cv, bv, a); break;
+        case 0: e = launch_decode_dt<0>(ctx, cv, bv, a); break;
+        case 1: e = launch_decode_dt<1>(ctx, cv, bv, a); break;
+        default: e = launch_decode_dt<2>(ctx, cv, bv, a); break;
     }
     ctx->launches++;
-    HY3A_CUDA(ctx, cudaGetLastError());
+    if (e != cudaSuccess) return hy3a_fail(ctx, HY3A_ECUDA, "decode launch: %s", cudaGetErrorString(e));
     return HY3A_OK;
 }
 
