@@ -63,13 +63,16 @@ __device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g,
             unsigned w = (unsigned)(c[0] & 0xFF) | ((unsigned)(c[1] & 0xFF) << 8) | ((unsigned)(c[2] & 0xFF) << 16) | ((unsigned)(c[3] & 0xFF) << 24);
             *reinterpret_cast<unsigned *>(page + hy3a_k_dim_off<1>(tok, d0)) = w;
         } else {
-            unsigned short u0 = (unsigned short)((c[0] & 0xFF) | ((c[1] & 0xFF) << 8));
-            unsigned short u1 = (unsigned short)((c[2] & 0xFF) | ((c[3] & 0xFF) << 8));
+            /* V codes are kept offset-binary (c + 128): the decode kernel's byte-permute conversion
+             * to fp16 then needs no sign fix-up; export converts back to two's complement          */
+            unsigned short u0 = (unsigned short)((((c[0] & 0xFF) | ((c[1] & 0xFF) << 8))) ^ 0x8080);
+            unsigned short u1 = (unsigned short)((((c[2] & 0xFF) | ((c[3] & 0xFF) << 8))) ^ 0x8080);
             *reinterpret_cast<unsigned short *>(page + g.v_off + hy3a_v_unit_off<1>(tok, d0)) = u0;
             *reinterpret_cast<unsigned short *>(page + g.v_off + hy3a_v_unit_off<1>(tok, d0 + 2)) = u1;
         }
     } else {
         unsigned short u = (unsigned short)((c[0] & 0xF) | ((c[1] & 0xF) << 4) | ((c[2] & 0xF) << 8) | ((c[3] & 0xF) << 12));
+        if (is_v) u ^= 0x8888;   /* V nibbles offset-binary (n + 8), as for INT8 */
         int off = is_v ? g.v_off + hy3a_v_unit_off<2>(tok, d0) : hy3a_k_dim_off<2>(tok, d0);
         *reinterpret_cast<unsigned short *>(page + off) = u;
     }
@@ -90,6 +93,10 @@ struct append_args {
 /* grid (10, n_rows), block 256: warp (blockIdx.x*8 + warp) in [0,80) = 64 Q, 8 K, 8 V heads. */
 template <int DT>
 __global__ void __launch_bounds__(256) hy3a_append_kernel(hy3a_cache_view cache, hy3a_batch_view batch, hy3a_rope_params rope, append_args a) {
+    /* programmatic dependent launch: let the next kernel start its prologue, then wait until the
+     * preceding kernel's results are complete (no-ops without the launch attribute)             */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int row = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hr = blockIdx.x * 8 + warp;
@@ -220,7 +227,8 @@ __global__ void hy3a_xport_kernel(hy3a_cache_view cache, int layer, int seq, int
     } else {
         int off = is_v ? g.v_off + hy3a_v_unit_off<2>(tok, d0) : hy3a_k_dim_off<2>(tok, d0); pp[0] = page + off; pp[1] = page + off + 1;
     }
-    for (int b = 0; b < sbytes; b++) { if (import) *pp[b] = sp[b]; else sp[b] = *pp[b]; }
+    const uint8_t flip = (is_v && DT != 0) ? (DT == 1 ? 0x80 : 0x88) : 0x00;   /* V codes are stored offset-binary */
+    for (int b = 0; b < sbytes; b++) { if (import) *pp[b] = sp[b] ^ flip; else sp[b] = *pp[b] ^ flip; }
     if (DT != 0 && q4 == 0) {
         uint8_t *sc = page + (is_v ? g.vs_off : g.ks_off) + tok * 2;
         if (import) {
@@ -230,7 +238,31 @@ __global__ void hy3a_xport_kernel(hy3a_cache_view cache, int layer, int seq, int
     }
 }
 
+/* Reset pages to the "all codes zero" state: zero bytes everywhere except the V code area of
+ * INT8/INT4 pages, whose offset-binary zero is 0x80 / 0x88.  grid = pages, block 256.       */
+__global__ void hy3a_init_pages_kernel(uint8_t *pool, size_t first_page, int page_bytes, int v_off, int v_end, unsigned flip_word) {
+    uint4 *page = reinterpret_cast<uint4 *>(pool + (first_page + blockIdx.x) * (size_t)page_bytes);
+    const int lo = v_off / 16, hi = v_end / 16;
+    for (int i = threadIdx.x; i < page_bytes / 16; i += blockDim.x) {
+        const unsigned w = (i >= lo && i < hi) ? flip_word : 0u;
+        page[i] = make_uint4(w, w, w, w);
+    }
+}
+
 } /* namespace */
+
+int hy3a_launch_init_pages(hy3a_ctx *ctx, size_t first_page, size_t n_pages) {
+    const hy3a_geom g = ctx->geom;
+    const unsigned flip = g.dtype == 1 ? 0x80808080u : (g.dtype == 2 ? 0x88888888u : 0u);
+    const int v_end = g.dtype == 0 ? g.page_bytes : g.ks_off;
+    for (size_t done = 0; done < n_pages;) {
+        size_t chunk = n_pages - done > 1048576 ? 1048576 : n_pages - done;
+        hy3a_init_pages_kernel<<<(unsigned)chunk, 256, 0, ctx->stream>>>(ctx->pool, first_page + done, g.page_bytes, g.v_off, v_end, flip);
+        HY3A_CUDA(ctx, cudaGetLastError());
+        done += chunk;
+    }
+    return HY3A_OK;
+}
 
 int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, const float *k_in, size_t k_stride,
                        const float *v_in, size_t v_stride, float *q_out, size_t q_out_stride, void *q_out16) {
@@ -238,16 +270,22 @@ int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_str
     a.q_in = q_in; a.k_in = k_in; a.v_in = v_in; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
     a.q_out = q_out; a.q_out_stride = q_out_stride; a.q_out16 = (__half *)q_out16;
     a.norm_w = ctx->d_norm_w + (size_t)layer * 2 * HY3A_D; a.eps = ctx->cfg.rms_eps; a.layer = layer;
-    dim3 grid(10, ctx->batch_n), block(256);
     hy3a_cache_view cv = hy3a_view(ctx);
     hy3a_batch_view bv = hy3a_bview(ctx);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(10, ctx->batch_n); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+    cudaError_t e;
     switch (ctx->cfg.kv_dtype) {
-        case 0: hy3a_append_kernel<0><<<grid, block, 0, ctx->stream>>>(cv, bv, ctx->rope, a); break;
-        case 1: hy3a_append_kernel<1><<<grid, block, 0, ctx->stream>>>(cv, bv, ctx->rope, a); break;
-        default: hy3a_append_kernel<2><<<grid, block, 0, ctx->stream>>>(cv, bv, ctx->rope, a); break;
+        case 0: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<0>, cv, bv, ctx->rope, a); break;
+        case 1: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<1>, cv, bv, ctx->rope, a); break;
+        default: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<2>, cv, bv, ctx->rope, a); break;
     }
     ctx->launches++;
-    HY3A_CUDA(ctx, cudaGetLastError());
+    HY3A_CUDA(ctx, e);
     return HY3A_OK;
 }
 

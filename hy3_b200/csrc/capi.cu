@@ -68,15 +68,35 @@ size_t hy3a_block_bytes(const hy3a_config *cfg) {
 
 int hy3a_decode_schedule(int n, const int *kv_lens, int kv_heads, int n_ctas, int cta, long long *total_units, long long *u0,
                          long long *u1) {
+    /* the same arithmetic as the head of hy3a_decode_kernel */
     if (n < 0 || kv_heads < 1 || n_ctas < 1 || cta < 0 || cta >= n_ctas) return HY3A_EINVAL;
-    long long pages = 0;
-    for (int i = 0; i < n; i++) pages += kv_lens[i] > 0 ? (kv_lens[i] + HY3A_PAGE_TOKENS - 1) / HY3A_PAGE_TOKENS : 0;
-    long long U = pages * kv_heads;
-    if (U < n_ctas) n_ctas = (int)U;   /* the kernel never uses more CTAs than units */
+    long long P = 0;
+    int rows_ne = 0;
+    for (int i = 0; i < n; i++) { long long p = kv_lens[i] > 0 ? (kv_lens[i] + HY3A_PAGE_TOKENS - 1) / HY3A_PAGE_TOKENS : 0; P += p; rows_ne += p > 0; }
+    const long long U = P * kv_heads;
     if (total_units) *total_units = U;
-    if (cta >= n_ctas) { if (u0) *u0 = U; if (u1) *u1 = U; return 0; }
-    if (u0) *u0 = (long long)cta * U / n_ctas;
-    if (u1) *u1 = (long long)(cta + 1) * U / n_ctas;
+    long long b = U, e = U;
+    if (U > 0 && (long long)n * kv_heads < n_ctas) {
+        const long long spare = (long long)n_ctas - (long long)rows_ne * kv_heads;
+        long long base = 0, pre = 0;
+        for (int r = 0; r < n; r++) {
+            long long p = kv_lens[r] > 0 ? (kv_lens[r] + HY3A_PAGE_TOKENS - 1) / HY3A_PAGE_TOKENS : 0;
+            if (p == 0) continue;
+            long long c = 1 + spare * p / (P * kv_heads);
+            if (c > p) c = p;
+            if (cta < base + kv_heads * c) {
+                long long idx = cta - base, hl = idx / c, k = idx % c, seg0 = kv_heads * pre + hl * p;
+                b = seg0 + k * p / c; e = seg0 + (k + 1) * p / c;
+                break;
+            }
+            base += kv_heads * c; pre += p;
+        }
+    } else if (U > 0) {
+        const int C = U < n_ctas ? (int)U : n_ctas;
+        if (cta < C) { b = (long long)cta * U / C; e = (long long)(cta + 1) * U / C; }
+    }
+    if (u0) *u0 = b;
+    if (u1) *u1 = e;
     return 0;
 }
 
@@ -88,7 +108,7 @@ void hy3a_destroy(hy3a_ctx *ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     cudaFree(ctx->pool); cudaFree(ctx->d_block_table); cudaFree(ctx->d_vs_max); cudaFree(ctx->d_inv_freq);
     cudaFree(ctx->d_norm_w); cudaFree(ctx->d_batch); cudaFree(ctx->d_partials); cudaFree(ctx->d_counters); cudaFree(ctx->d_err);
-    cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v);
+    cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v); cudaFree(ctx->d_trace);
     if (ctx->h_ring) cudaFreeHost(ctx->h_ring);
     if (ctx->h_err) cudaFreeHost(ctx->h_err);
     for (int i = 0; i < HY3A_RING_SLOTS; i++) if (ctx->ring_ev[i]) cudaEventDestroy(ctx->ring_ev[i]);
@@ -136,6 +156,9 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->decode_ctas = prop.multiProcessorCount;
     { const char *e = getenv("HY3A_DECODE_CTAS"); if (e && atoi(e) > 0) ctx->decode_ctas = atoi(e); }
+    if (ctx->decode_ctas > hy3a_decode_max_ctas()) ctx->decode_ctas = hy3a_decode_max_ctas();
+    if (ctx->decode_ctas > 512) ctx->decode_ctas = 512;
+    { const char *e = getenv("HY3A_NO_PDL"); ctx->use_pdl = !(e && atoi(e)); }
     {   /* ring depth: as many pages as fit in shared memory beside the merge buffers, at most 8 */
         ctx->decode_stages = hy3a_decode_ring_capacity(ctx->geom.page_bytes, cfg->max_batch);
         const char *e = getenv("HY3A_DECODE_STAGES");
@@ -148,7 +171,9 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     const size_t block_bytes = (size_t)cfg->n_layers * cfg->kv_head_count * ctx->geom.page_bytes;
     ctx->pool_bytes = block_bytes * (size_t)cfg->max_blocks;
     CREATE_CUDA(cudaMalloc(&ctx->pool, ctx->pool_bytes));
-    CREATE_CUDA(cudaMemsetAsync(ctx->pool, 0, ctx->pool_bytes, ctx->stream));
+    if (hy3a_launch_init_pages(ctx, 0, (size_t)cfg->max_blocks * cfg->n_layers * cfg->kv_head_count)) {
+        hy3a_fail(NULL, HY3A_ECUDA, "%s", ctx->err); hy3a_destroy(ctx); return HY3A_ECUDA;
+    }
     const size_t bt = (size_t)cfg->max_seqs * cfg->max_blocks_per_seq;
     CREATE_CUDA(cudaMalloc(&ctx->d_block_table, bt * sizeof(int)));
     CREATE_CUDA(cudaMemsetAsync(ctx->d_block_table, 0, bt * sizeof(int), ctx->stream));
@@ -161,6 +186,8 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     CREATE_CUDA(cudaMalloc(&ctx->d_partials, ctx->partial_records * 8 * HY3A_PARTIAL_FLOATS * sizeof(float)));
     CREATE_CUDA(cudaMalloc(&ctx->d_counters, (size_t)cfg->max_batch * cfg->kv_head_count * sizeof(unsigned)));
     CREATE_CUDA(cudaMemsetAsync(ctx->d_counters, 0, (size_t)cfg->max_batch * cfg->kv_head_count * sizeof(unsigned), ctx->stream));
+    CREATE_CUDA(cudaMalloc(&ctx->d_trace, (size_t)512 * 64 * sizeof(unsigned long long)));
+    CREATE_CUDA(cudaMemsetAsync(ctx->d_trace, 0, (size_t)512 * 64 * sizeof(unsigned long long), ctx->stream));
     CREATE_CUDA(cudaMalloc(&ctx->d_err, HY3A_ERR_WORDS * sizeof(unsigned)));
     CREATE_CUDA(cudaMemsetAsync(ctx->d_err, 0, HY3A_ERR_WORDS * sizeof(unsigned), ctx->stream));
     CREATE_CUDA(cudaHostAlloc((void **)&ctx->h_err, HY3A_ERR_WORDS * sizeof(unsigned), cudaHostAllocDefault));

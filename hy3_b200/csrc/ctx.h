@@ -65,6 +65,7 @@ struct hy3a_ctx {
     unsigned int *d_counters; /* decode scratch: [max_batch*kv_heads] arrival counters (self-resetting) */
     void *d_pf_k, *d_pf_v; /* prefill: fp16 staging of dequantised K / V pages (INT8/INT4 caches) */
     size_t pf_bytes;
+    unsigned long long *d_trace; /* [512][64] timestamps written by trace builds of the decode kernel */
     unsigned int *d_err;  /* HY3A_ERR_WORDS words: kernels record bounded-wait timeouts / bad indices here */
     size_t partial_records;
 
@@ -81,6 +82,7 @@ struct hy3a_ctx {
     unsigned int *h_err;  /* pinned */
     int batch_n;
     int decode_ctas;
+    int use_pdl;          /* launch kernels with programmatic stream serialization (HY3A_NO_PDL=1 turns it off) */
     int decode_stages;    /* pages in the decode kernel's shared-memory ring; < 2 selects the direct-load variant */
 
     hy3a_rope_params rope;
@@ -99,7 +101,9 @@ int hy3a_launch_export(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint8_t
 int hy3a_launch_fill_random(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint64_t seed);
 int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq, const void *q16, float *out,
                         size_t out_stride);
+int hy3a_launch_init_pages(hy3a_ctx *ctx, size_t first_page, size_t n_pages);
 int hy3a_decode_ring_capacity(int page_bytes, int max_batch);
+int hy3a_decode_max_ctas(void);
 int hy3a_fail(hy3a_ctx *ctx, int code, const char *fmt, ...);
 
 static inline hy3a_cache_view hy3a_view(const hy3a_ctx *c) {

@@ -7,27 +7,32 @@
  * an 83 KB stride.  Here a warp processes 16 tokens of one KV head for ALL 8 query heads
  * of the group at once, on tensor cores, so each KV byte is read exactly once:
  *
- *   S[16 x 8]  = Qsplit[16 x 128] . K^T      mma.sync m16n8k16, rows 0-7 = fp16(q) of the 8
- *                                            heads, rows 8-15 = the fp16 residual q - fp16(q)
- *                                            (M=16 is the MMA's minimum, so the second half
- *                                            of the tile buys ~fp32-accurate queries for free)
- *   O[16 x 128] += Psplit[16 x 16] . V       same trick: rows 8-15 carry the fp16 residual of P
+ *   S[16 x 8]   = Q2[16 x 128] . K^T    rows 0-7 = the 8 heads, rows 8-15 = a residual of the
+ *                                       same 8 queries (M=16 is the MMA minimum, so the second
+ *                                       half of the tile buys near-fp32 queries for free).
+ *                                       INT8/INT4 caches: integer MMA (m16n8k32.s8) directly on
+ *                                       the stored codes -- Q is split into two int8 digits
+ *                                       (q ~ sq*(hi + lo/254)), the products are exact, and no
+ *                                       per-element conversion of K is needed at all.
+ *                                       FP16 cache: m16n8k16.f16 with Q = fp16 + fp16 residual.
+ *   O[16 x 128] += P[16 x 16] . V       m16n8k16.f16; INT8/INT4 codes become fp16 exactly with one
+ *                                       byte-permute (or lop3) + one fp16 subtract per pair.
  *
- * INT8/INT4 codes are converted to fp16 exactly (|code| <= 127) in registers with
- * byte-permute / lop3 magic-number tricks; the per-token scales are applied once per
- * score (K) and once per probability (V), never per element.  The contraction dimension
- * of Q.K^T and the output dimension of P.V are permuted so that every thread's MMA
- * operands are exactly the 16-byte chunks it loads -- no shuffles, no transposes.
+ * The per-token scales are applied once per score (K) and once per probability (V), never
+ * per element.  The contraction dimension of Q.K^T and the output dimension of P.V are
+ * permuted so that every thread's MMA operands are exactly the 16-byte chunks it loads.
  *
  * Scheduling: unit = one 128-token page of one (batch row, KV head); units are laid out
- * row-major, head, page and cut into `gridDim.x` contiguous ranges, so one launch shape
+ * row-major, head, page and cut into contiguous ranges, one per CTA, so one launch shape
  * serves every length (lengths come from device memory; nothing is baked into a captured
- * graph, cf. hy3_gpu.cu:774-789).  A CTA's 8 warps each take 16 tokens of the current
- * page.  The piece a CTA computes for a (row, head) segment is merged in shared memory;
- * if the segment spans several CTAs each writes an {m, l, acc} record and the LAST CTA to
- * arrive (atomic counter) folds them -- the LSE-merge epilogue, no second launch.
+ * graph, cf. hy3_gpu.cu:774-789).  A producer warp streams the CTA's pages into a shared-
+ * memory ring with bulk asynchronous copies (cp.async.bulk + mbarrier transaction counts);
+ * the consumer warps take the 16-token granules of the pages round-robin.  The piece a CTA
+ * computes for a (row, head) segment is folded in shared memory; if the segment spans
+ * several CTAs each writes an {m, l, acc} record and the LAST CTA to arrive (atomic
+ * counter) folds them -- the LSE-merge epilogue, no second launch.
  *
- * Roofline: HBM.  Algorithmic bytes per (token, KV head): 4 x 128 (FP16), 260 (INT8),
+ * Roofline: HBM.  Algorithmic bytes per (token, KV head): 512 (FP16), 260 (INT8),
  * 132 (INT4); per token and layer x8.
  */
 #include <cuda_fp16.h>
@@ -37,15 +42,18 @@
 
 namespace {
 
-constexpr int kWarps = HY3A_DECODE_WARPS;
+constexpr int kWarps = HY3A_DECODE_WARPS;              /* consumer warps */
+static_assert(kWarps >= 8, "the Q packing and the reductions use the first 8 consumer warps");
 constexpr int kThreads = kWarps * 32;
 constexpr int kFixedO = kWarps * 8 * HY3A_D * 4;
 constexpr int kFixedML = ((kWarps * 8 * 2 * 4) + 127) / 128 * 128;
 constexpr int kFixedQ = 8 * 32 * 16;
 constexpr int kFixed = kFixedO + kFixedML + kFixedQ;   /* bytes of shared memory in front of the page-count prefix */
 constexpr int kSmemMax = 232448 - 1024;                /* opt-in limit per block minus the driver's reserve */
+constexpr bool kPSplit = true;                         /* carry the fp16 residual of P in MMA rows 8-15 */
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.f;               /* lazy rescale: the running max may lag by 2^8 */
 
 __device__ __forceinline__ uint4 ld16(const uint8_t *p) {
     uint4 v;
@@ -83,8 +91,13 @@ __device__ __forceinline__ float2 unpack_h2(unsigned v) {
 }
 __device__ __forceinline__ void mma16816(float c[4], const unsigned a[4], unsigned b0, unsigned b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma16832(int c[4], const uint4 &a, unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ float ex2(float x) {
     float r;
@@ -92,33 +105,36 @@ __device__ __forceinline__ float ex2(float x) {
     return r;
 }
 
-/* ---- exact integer-code -> fp16x2 conversions ---------------------------------------
- * INT8: xs = word ^ 0x80808080 turns each two's-complement byte into c+128; placing it
- * under the exponent byte 0x64 gives the fp16 number 1024 + (c+128); subtracting 1152
- * leaves c exactly.  sel picks which two bytes become the (low, high) halves.           */
-__device__ __forceinline__ unsigned cvt_i8(unsigned xs, unsigned sel) { return hsub2(prmt(xs, 0x64646464u, sel), 0x64806480u); }
-/* INT4: xs = word ^ 0x88888888 turns each nibble into n+8.  Nibbles (i, i+4) become one
- * fp16x2.  Low-position nibbles: (xs & 0x000f000f) | 0x6400 = 1024 + (n+8), minus 1032.
- * High-position nibbles: (xs & 0x00f000f0) | 0x6400 = 1024 + 16(n+8); *1/16 - 72 = n.    */
-__device__ __forceinline__ unsigned cvt_i4_lo(unsigned xs) {
+/* ---- exact integer-code -> fp16x2 conversions of V --------------------------------------
+ * V codes are stored offset-binary (INT8: c+128, INT4: n+8; see append.cu), so that no sign
+ * fix-up is needed here.  INT8: placing a byte under the exponent byte 0x64 gives the fp16
+ * number 1024 + (c+128); subtracting 1152 leaves c exactly.  sel picks which two bytes
+ * become the (low, high) halves.                                                          */
+__device__ __forceinline__ unsigned cvt_u8(unsigned x, unsigned sel) { return hsub2(prmt(x, 0x64646464u, sel), 0x64806480u); }
+/* INT4: nibbles (i, i+4) become one fp16x2.  Low positions: (x & 0x000f000f) | 0x6400 =
+ * 1024 + (n+8), minus 1032.  High positions: (x & 0x00f000f0) | 0x6400 = 1024 + 16(n+8);
+ * times 1/16 minus 72 = n.                                                               */
+__device__ __forceinline__ unsigned cvt_u4_lo(unsigned x) {
     unsigned v;
-    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(v) : "r"(xs));
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(v) : "r"(x));
     return hsub2(v, 0x64086408u);
 }
-__device__ __forceinline__ unsigned cvt_i4_hi(unsigned xs) {
+__device__ __forceinline__ unsigned cvt_u4_hi(unsigned x) {
     unsigned v;
-    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(v) : "r"(xs));
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(v) : "r"(x));
     return hfma2(v, 0x2c002c00u /* 1/16 */, 0xd480d480u /* -72 */);
 }
 
-/* ---- contraction-dimension map of Q.K^T ---------------------------------------------
- * For k-step j (0..7) and thread-in-group tig, the four MMA k-slots
- * (2tig, 2tig+1, 2tig+8, 2tig+9) carry head dims kdim(j, tig, 0..3): exactly the dims
- * whose codes the thread gets out of its own 16-byte loads.                             */
-template <int DT> __device__ __forceinline__ int kdim(int j, int tig, int s) {
-    if (DT == 1) { int c = tig + 4 * (j >> 2); return 16 * c + 4 * (j & 3) + s; }
-    if (DT == 2) { int base = 32 * tig + 8 * (j >> 1) + 2 * (j & 1); return base + (s >> 1) + 4 * (s & 1); }
-    { int c = tig + 4 * (j >> 1); return 8 * c + 4 * (j & 1) + s; }
+/* ---- contraction-dimension maps of Q.K^T -------------------------------------------------
+ * FP16 cache (m16n8k16): for k-step j (0..7) the four MMA k-slots (2tig, 2tig+1, 2tig+8,
+ * 2tig+9) of thread-in-group tig carry head dims kdim16(j, tig, 0..3).
+ * INT8/INT4 caches (m16n8k32): for k-step kk (0..3) the eight k-slots (4tig..4tig+3,
+ * 16+4tig..16+4tig+3) carry head dims kdim32<DT>(kk, tig, 0..7).  In both cases these are
+ * exactly the dims whose codes the thread gets out of its own 16-byte loads.              */
+__device__ __forceinline__ int kdim16(int j, int tig, int s) { int c = tig + 4 * (j >> 1); return 8 * c + 4 * (j & 1) + s; }
+template <int DT> __device__ __forceinline__ int kdim32(int kk, int tig, int s) {
+    if (DT == 1) return 16 * (tig + 4 * (s >> 2)) + 4 * kk + (s & 3);   /* chunk tig / tig+4, word kk */
+    return 32 * tig + 8 * kk + 2 * (s & 3) + (s >> 2);                   /* word kk: even nibbles, then odd nibbles */
 }
 /* ---- output-dimension map of P.V: n-block jn (0..15), column n (0..7) -> head dim. */
 template <int DT> __device__ __forceinline__ int vdim(int jn, int n) {
@@ -126,7 +142,15 @@ template <int DT> __device__ __forceinline__ int vdim(int jn, int n) {
     return 8 * n + 64 * (jn >> 3) + (jn & 7);
 }
 
+#ifdef HY3A_DECODE_TRACE
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TRACE(slot) do { if (lane == 0 && (slot) < 64) a.trace[(size_t)blockIdx.x * 64 + (slot)] = gtime(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
+
 struct decode_args {
+    unsigned long long *trace; /* [gridDim.x][64] timestamps (trace builds only) */
     const float *q;
     size_t q_stride;
     float *out;
@@ -137,11 +161,11 @@ struct decode_args {
     unsigned int *err;
     int layer;
     int stages;           /* staged variant: pages in the shared-memory ring (2..8) */
-    int prefix_bytes;     /* staged variant: bytes reserved for the page-count prefix */
+    int prefix_bytes;     /* bytes reserved for the page-count prefix */
 };
 
 struct warp_state {
-    float m;      /* running max (base-2 logits), identical in the 4 lanes of a head */
+    float m;      /* reference max (base-2 logits), identical in the 4 lanes of a head; may lag the true max by 2^8 */
     float l;      /* this lane's share of the denominator */
     float o[16][4];
 };
@@ -174,7 +198,7 @@ __device__ __forceinline__ segment locate(const int *s_prefix, const hy3a_batch_
     return sg;
 }
 
-/* ---- shared-memory / mbarrier / bulk-copy primitives (staged variant) ---------------- */
+/* ---- shared-memory / mbarrier / bulk-copy primitives ---------------------------------- */
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint4 lds16(unsigned addr) {
     uint4 v;
@@ -205,7 +229,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     if (mbar_test(bar, parity)) return true;
     for (unsigned i = 0; i < (1u << 22); i++) {
         if (mbar_test(bar, parity)) return true;
-        if ((i & 255u) == 255u) { if (*abort_flag) return false; __nanosleep(64); }
+        if ((i & 63u) == 63u) { if (*abort_flag) return false; __nanosleep(32); }
     }
     *abort_flag = 1;
     if (atomicCAS(err, 0u, 1u) == 0u) err[1] = where;
@@ -214,17 +238,17 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
 /* One 16-token granule of one warp: loads, S = Q.K^T, online softmax, O += P.V.
- * SM: operands come from a shared-memory copy of the page (addresses are 32-bit shared
- * addresses) instead of global memory.                                                  */
-template <int DT, bool SM>
-__device__ __forceinline__ void granule(warp_state &st, unsigned sq, const uint8_t *gpage, unsigned spage, const hy3a_geom &geom,
+ * SM: operands come from a shared-memory copy of the page (32-bit shared addresses) instead
+ * of global memory.  FULL: all 16 tokens are valid (no masking).  sq: shared address of this
+ * lane's Q fragments; qf: score factor of this lane's head (integer-MMA path).             */
+template <int DT, bool SM, bool FULL>
+__device__ __forceinline__ void granule(warp_state &st, unsigned sq, float qf, const uint8_t *gpage, unsigned spage, const hy3a_geom &geom,
                                         const int (&k_off)[2][4], const int (&v_off)[8], const int (&sc_off)[2], int gi, int tig, int valid,
                                         float pscale) {
-    /* page-relative byte offsets of granule gi (16 tokens = 16 K rows = 8 V pair-rows) */
-    const int gk = gi * 16 * geom.k_row, gv = geom.v_off + gi * (DT == 0 ? 16 : 8) * geom.v_prow, gs = gi * 32;
-    gpage += 0;
     constexpr int NK = DT == 0 ? 4 : (DT == 1 ? 2 : 1);
     constexpr int NV = DT == 0 ? 8 : (DT == 1 ? 4 : 2);
+    /* page-relative byte offsets of granule gi (16 tokens = 16 K rows = 8 V pair-rows) */
+    const int gk = gi * 16 * geom.k_row, gv = geom.v_off + gi * (DT == 0 ? 16 : 8) * geom.v_prow, gs = gi * 32;
     uint4 kr[2][NK];
 #pragma unroll
     for (int nb = 0; nb < 2; nb++) {
@@ -242,42 +266,16 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, const uint8
     uint4 vr[NV];
 #pragma unroll
     for (int i = 0; i < NV; i++) vr[i] = SM ? lds16(spage + gv + v_off[i]) : ld16(gpage + gv + v_off[i]);
-    /* Q operand fragments of this thread for the 8 k-steps, pre-packed in shared memory */
-    unsigned qa[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; j++) { uint4 t = lds16(sq + j * 512); qa[j][0] = t.x; qa[j][1] = t.y; qa[j][2] = t.z; qa[j][3] = t.w; }
 
-    /* ---- S = Q.K^T for the two 8-token n-blocks; even and odd k-steps accumulate separately so
-     * that four independent MMA chains are in flight instead of two                              */
-    float sc[2][4], sd[2][4];
+    /* ---- raw scores r[nb][e] of head g for tokens 16gi + 8nb + 2tig + e (before the K scale) */
+    float r[2][2];
+    if (DT == 0) {
+        unsigned qa[8][4];
 #pragma unroll
-    for (int nb = 0; nb < 2; nb++) { sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f; sd[nb][0] = sd[nb][1] = sd[nb][2] = sd[nb][3] = 0.f; }
-    if (DT == 1) {
+        for (int j = 0; j < 8; j++) { uint4 t = lds16(sq + j * 512); qa[j][0] = t.x; qa[j][1] = t.y; qa[j][2] = t.z; qa[j][3] = t.w; }
+        float sc[2][4], sd[2][4];   /* even / odd k-steps accumulate separately: four independent MMA chains */
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-#pragma unroll
-            for (int r = 0; r < 4; r += 2) {
-#pragma unroll
-                for (int nb = 0; nb < 2; nb++) {
-                    const unsigned w0 = (r == 0 ? kr[nb][i].x : kr[nb][i].z) ^ 0x80808080u;
-                    const unsigned w1 = (r == 0 ? kr[nb][i].y : kr[nb][i].w) ^ 0x80808080u;
-                    mma16816(sc[nb], qa[4 * i + r], cvt_i8(w0, 0x4140u), cvt_i8(w0, 0x4342u));
-                    mma16816(sd[nb], qa[4 * i + r + 1], cvt_i8(w1, 0x4140u), cvt_i8(w1, 0x4342u));
-                }
-            }
-        }
-    } else if (DT == 2) {
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-#pragma unroll
-            for (int nb = 0; nb < 2; nb++) {
-                const unsigned w = (r == 0 ? kr[nb][0].x : (r == 1 ? kr[nb][0].y : (r == 2 ? kr[nb][0].z : kr[nb][0].w)));
-                const unsigned xs = w ^ 0x88888888u, xh = xs >> 8;
-                mma16816(sc[nb], qa[2 * r], cvt_i4_lo(xs), cvt_i4_hi(xs));
-                mma16816(sd[nb], qa[2 * r + 1], cvt_i4_lo(xh), cvt_i4_hi(xh));
-            }
-        }
-    } else {
+        for (int nb = 0; nb < 2; nb++) { sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f; sd[nb][0] = sd[nb][1] = sd[nb][2] = sd[nb][3] = 0.f; }
 #pragma unroll
         for (int i = 0; i < NK; i++) {
 #pragma unroll
@@ -286,28 +284,61 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, const uint8
                 mma16816(sd[nb], qa[2 * i + 1], kr[nb][i].z, kr[nb][i].w);
             }
         }
-    }
 #pragma unroll
-    for (int nb = 0; nb < 2; nb++) { sc[nb][0] += sd[nb][0]; sc[nb][1] += sd[nb][1]; sc[nb][2] += sd[nb][2]; sc[nb][3] += sd[nb][3]; }
-    /* ---- scores of head g for tokens 16w + 8nb + 2tig + e */
+        for (int nb = 0; nb < 2; nb++) { r[nb][0] = (sc[nb][0] + sd[nb][0]) + (sc[nb][2] + sd[nb][2]); r[nb][1] = (sc[nb][1] + sd[nb][1]) + (sc[nb][3] + sd[nb][3]); }
+    } else {
+        uint4 qa[4];
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) qa[kk] = lds16(sq + kk * 512);
+        int ce[2][4], co[2][4];     /* even / odd k-steps: four independent integer-MMA chains */
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++) { ce[nb][0] = ce[nb][1] = ce[nb][2] = ce[nb][3] = 0; co[nb][0] = co[nb][1] = co[nb][2] = co[nb][3] = 0; }
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) {
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++) {
+                unsigned b0, b1;
+                if (DT == 1) {
+                    b0 = kk == 0 ? kr[nb][0].x : (kk == 1 ? kr[nb][0].y : (kk == 2 ? kr[nb][0].z : kr[nb][0].w));
+                    b1 = kk == 0 ? kr[nb][NK - 1].x : (kk == 1 ? kr[nb][NK - 1].y : (kk == 2 ? kr[nb][NK - 1].z : kr[nb][NK - 1].w));
+                } else {
+                    /* two's-complement nibbles: moving a nibble to the top of its byte gives 16 x code as int8 */
+                    const unsigned w = kk == 0 ? kr[nb][0].x : (kk == 1 ? kr[nb][0].y : (kk == 2 ? kr[nb][0].z : kr[nb][0].w));
+                    b0 = (w << 4) & 0xF0F0F0F0u;
+                    b1 = w & 0xF0F0F0F0u;
+                }
+                imma16832((kk & 1) ? co[nb] : ce[nb], qa[kk], b0, b1);
+            }
+        }
+        /* rows 0-7 carry the high digit of q, rows 8-15 the low digit: q ~ sq*(hi + lo/254) */
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++) {
+            r[nb][0] = (float)((ce[nb][0] + co[nb][0]) * 254 + (ce[nb][2] + co[nb][2])) * qf;
+            r[nb][1] = (float)((ce[nb][1] + co[nb][1]) * 254 + (ce[nb][3] + co[nb][3])) * qf;
+        }
+    }
+    /* ---- logits (base 2) and V scales */
     float s[2][2], vs[2][2];
 #pragma unroll
     for (int nb = 0; nb < 2; nb++) {
         float2 kf = make_float2(1.f, 1.f), vf = make_float2(1.f, 1.f);
         if (DT != 0) { kf = unpack_h2(ksw[nb]); vf = unpack_h2(vsw[nb]); }
-        int t0 = 16 * gi + 8 * nb + 2 * tig;
-        float r0 = sc[nb][0] + sc[nb][2], r1 = sc[nb][1] + sc[nb][3];
-        s[nb][0] = (t0 < valid) ? r0 * kf.x : -INFINITY;
-        s[nb][1] = (t0 + 1 < valid) ? r1 * kf.y : -INFINITY;
-        vs[nb][0] = (t0 < valid) ? vf.x * pscale : 0.f;
-        vs[nb][1] = (t0 + 1 < valid) ? vf.y * pscale : 0.f;
+        const int t0 = 16 * gi + 8 * nb + 2 * tig;
+        s[nb][0] = (FULL || t0 < valid) ? r[nb][0] * kf.x : -INFINITY;
+        s[nb][1] = (FULL || t0 + 1 < valid) ? r[nb][1] * kf.y : -INFINITY;
+        vs[nb][0] = (FULL || t0 < valid) ? vf.x * pscale : 0.f;
+        vs[nb][1] = (FULL || t0 + 1 < valid) ? vf.y * pscale : 0.f;
     }
+    /* ---- online softmax with a lazily updated reference max: O and l are only rescaled when
+     * the granule's max exceeds the reference by more than 2^8; until then p <= 2^8, which the
+     * fp16 range of P has room for (pscale leaves 2^8 of headroom).                           */
     float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(st.m, mx); /* finite: token 16w of this granule is valid */
-    if (__any_sync(0xffffffffu, m_new > st.m)) {
-        const float alpha = ex2(st.m - m_new); /* 0 on the first granule (m = -inf) */
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));   /* finite: token 16gi of this granule is valid */
+    const bool grow = mx > st.m + kRescaleThreshold;       /* also true while st.m == -inf */
+    if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = grow ? mx : st.m;
+        const float alpha = ex2(st.m - m_new);             /* 0 on the first granule (m = -inf), 1 if unchanged */
         st.l *= alpha;
 #pragma unroll
         for (int jn = 0; jn < 16; jn++) { st.o[jn][0] *= alpha; st.o[jn][1] *= alpha; st.o[jn][2] *= alpha; st.o[jn][3] *= alpha; }
@@ -320,16 +351,20 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, const uint8
         for (int nb = 0; nb < 2; nb++) {
 #pragma unroll
             for (int e = 0; e < 2; e++) {
-                float pe = ex2(s[nb][e] - st.m); /* -inf -> 0 */
+                const float pe = ex2(s[nb][e] - st.m); /* -inf -> 0 */
                 st.l += pe;
                 w[nb][e] = pe * vs[nb][e];
             }
         }
         pa[0] = pack_h2(w[0][0], w[0][1]);
         pa[2] = pack_h2(w[1][0], w[1][1]);
-        float2 h0 = unpack_h2(pa[0]), h1 = unpack_h2(pa[2]);
-        pa[1] = pack_h2(w[0][0] - h0.x, w[0][1] - h0.y);
-        pa[3] = pack_h2(w[1][0] - h1.x, w[1][1] - h1.y);
+        if (kPSplit) {
+            float2 h0 = unpack_h2(pa[0]), h1 = unpack_h2(pa[2]);
+            pa[1] = pack_h2(w[0][0] - h0.x, w[0][1] - h0.y);
+            pa[3] = pack_h2(w[1][0] - h1.x, w[1][1] - h1.y);
+        } else {
+            pa[1] = pa[3] = 0u;
+        }
     }
     /* ---- O += P.V over 16 n-blocks of 8 output dims */
     if (DT == 1) {
@@ -339,9 +374,8 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, const uint8
             unsigned b4[4] = {vr[2 + half].x, vr[2 + half].y, vr[2 + half].z, vr[2 + half].w};
 #pragma unroll
             for (int k = 0; k < 4; k++) {
-                unsigned xa = a4[k] ^ 0x80808080u, xb = b4[k] ^ 0x80808080u;
-                mma16816(st.o[8 * half + 2 * k], pa, cvt_i8(xa, 0x4240u), cvt_i8(xb, 0x4240u));
-                mma16816(st.o[8 * half + 2 * k + 1], pa, cvt_i8(xa, 0x4341u), cvt_i8(xb, 0x4341u));
+                mma16816(st.o[8 * half + 2 * k], pa, cvt_u8(a4[k], 0x4240u), cvt_u8(b4[k], 0x4240u));
+                mma16816(st.o[8 * half + 2 * k + 1], pa, cvt_u8(a4[k], 0x4341u), cvt_u8(b4[k], 0x4341u));
             }
         }
     } else if (DT == 2) {
@@ -349,11 +383,11 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, const uint8
         unsigned b4[4] = {vr[1].x, vr[1].y, vr[1].z, vr[1].w};
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            unsigned xa = a4[k] ^ 0x88888888u, xb = b4[k] ^ 0x88888888u, xah = xa >> 8, xbh = xb >> 8;
-            mma16816(st.o[4 * k + 0], pa, cvt_i4_lo(xa), cvt_i4_lo(xb));
-            mma16816(st.o[4 * k + 1], pa, cvt_i4_hi(xa), cvt_i4_hi(xb));
-            mma16816(st.o[4 * k + 2], pa, cvt_i4_lo(xah), cvt_i4_lo(xbh));
-            mma16816(st.o[4 * k + 3], pa, cvt_i4_hi(xah), cvt_i4_hi(xbh));
+            const unsigned xa = a4[k], xb = b4[k], xah = xa >> 8, xbh = xb >> 8;
+            mma16816(st.o[4 * k + 0], pa, cvt_u4_lo(xa), cvt_u4_lo(xb));
+            mma16816(st.o[4 * k + 1], pa, cvt_u4_hi(xa), cvt_u4_hi(xb));
+            mma16816(st.o[4 * k + 2], pa, cvt_u4_lo(xah), cvt_u4_lo(xbh));
+            mma16816(st.o[4 * k + 3], pa, cvt_u4_hi(xah), cvt_u4_hi(xbh));
         }
     } else {
 #pragma unroll
@@ -372,10 +406,9 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, const uint8
     }
 }
 
-/* DIRECT variant: 8 warps, operands fetched straight from global memory with 128-bit loads.
- * STAGED variant: 8 consumer warps + 1 producer warp; the producer streams whole pages into a
- * shared-memory ring with bulk asynchronous copies (cp.async.bulk + mbarrier transaction
- * counts), consumers read their fragments from the ring.  Same arithmetic, same results.  */
+/* DIRECT variant (STAGED=false): operands fetched straight from global memory with 128-bit
+ * loads (no ring, no producer).  STAGED variant: kWarps consumer warps + 1 producer warp.
+ * Same arithmetic, same results.                                                          */
 template <int DT, bool STAGED>
 __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_kernel(hy3a_cache_view cache, hy3a_batch_view batch, decode_args a) {
     /* dynamic shared memory: [s_o | s_ml | s_q | page-count prefix | full[8] empty[8] | ring of pages] */
@@ -383,6 +416,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     float (*s_o)[8][HY3A_D] = reinterpret_cast<float (*)[8][HY3A_D]>(s_dyn);                       /* per-warp unnormalised outputs */
     float (*s_ml)[8][2] = reinterpret_cast<float (*)[8][2]>(s_dyn + kFixedO);                      /* per-warp {m, l} */
     uint4 (*s_q)[32] = reinterpret_cast<uint4 (*)[32]>(s_dyn + kFixedO + kFixedML);                /* Q fragments: [k-step][lane] */
+    __shared__ float s_qf[8];
     __shared__ int s_flag;
     __shared__ int s_abort;
 
@@ -391,6 +425,10 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     const int g = lane >> 2, tig = lane & 3;
     const int n = batch.n, G = cache.kv_heads;
     const int cta = blockIdx.x;
+    if (warp == 0) TRACE(0);
+    /* Programmatic dependent launch: the next kernel in the stream may begin its own prologue now.
+     * (No-ops when the launch does not carry the attribute.)                                        */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     int *s_prefix = reinterpret_cast<int *>(s_dyn + kFixed);
     const unsigned bar_base = smem_u32(s_dyn + kFixed + a.prefix_bytes);
     const unsigned ring_base = bar_base + 128;
@@ -409,7 +447,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
         }
     }
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 0 && n > 1) {
         int carry = 0;
         for (int base = 0; base < n; base += 32) {
             int i = base + lane;
@@ -425,10 +463,17 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     }
     __syncthreads();
 
+    const long long U = (long long)G * s_prefix[n];
+    /* Everything above reads only what the host wrote (batch descriptor).  From here on the kernel
+     * touches memory that the preceding kernel in the stream may produce (queries, the newest KV
+     * slot, scratch records), so wait for it -- except the producer lane, which first starts the
+     * copies of pages that lie wholly below the newest slot (append-only cache: immutable).       */
+    const bool is_producer = STAGED && warp == kWarps;
+    if (!is_producer) asm volatile("griddepcontrol.wait;" ::: "memory");
     /* rows with no keys on this rank: zero output / empty partial (hy3_gpu.cu:197-199) */
     for (int i = cta; i < n; i += gridDim.x) {
         if (s_prefix[i + 1] != s_prefix[i]) continue;
-        for (int e = tid; e < G * 8 * HY3A_D; e += blockDim.x) {
+        for (int e = tid; e < G * 8 * HY3A_D && !is_producer; e += kThreads) {
             int hq = e / HY3A_D, d = e % HY3A_D;
             if (a.user_partials) {
                 float *p = a.user_partials + ((size_t)i * G * 8 + hq) * HY3A_PARTIAL_FLOATS;
@@ -440,18 +485,54 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
         }
     }
 
-    const long long U = (long long)G * s_prefix[n];
-    /* never more CTAs than units, so that every participating CTA owns at least one unit and the
-     * CTAs that share a segment are exactly the contiguous range [c_first, c_last]              */
-    const int C = (long long)gridDim.x < U ? (int)gridDim.x : (int)U;
-    if (cta >= C) return;
-    const long long u_begin = (long long)cta * U / C, u_end = (long long)(cta + 1) * U / C;
+    if (U == 0) return;
+    /* Two ways to cut the units into per-CTA ranges:
+     *  - few segments (n*G < grid): every segment gets its own whole number of CTAs, roughly in
+     *    proportion to its pages, so no CTA straddles two segments (a straddling CTA pays the
+     *    query set-up and the fold twice and becomes the critical path of a small batch);
+     *  - many segments: one contiguous, equally sized range per CTA over all units.
+     * In both, never more CTAs than units, and the CTAs sharing a segment are contiguous.       */
+    const bool aligned = (long long)n * G < (long long)gridDim.x;
+    int C = (long long)gridDim.x < U ? (int)gridDim.x : (int)U;
+    long long u_begin, u_end;
+    int al_first = 0, al_pieces = 1;
+    if (aligned) {
+        int rows_ne = 0;
+        for (int r = 0; r < n; r++) rows_ne += (s_prefix[r + 1] != s_prefix[r]);
+        const long long spare = (long long)gridDim.x - (long long)rows_ne * G, P = s_prefix[n];
+        int base = 0;
+        bool found = false;
+        u_begin = u_end = 0;
+        for (int r = 0; r < n && !found; r++) {
+            const int p = s_prefix[r + 1] - s_prefix[r];
+            if (p == 0) continue;
+            int c = 1 + (int)(spare * p / (P * G));
+            c = c < p ? c : p;
+            if (cta < base + G * c) {
+                const int idx = cta - base, hl = idx / c, k = idx % c;
+                const long long seg0 = (long long)G * s_prefix[r] + (long long)hl * p;
+                u_begin = seg0 + (long long)k * p / c;
+                u_end = seg0 + (long long)(k + 1) * p / c;
+                al_first = base + hl * c;
+                al_pieces = c;
+                found = true;
+            }
+            base += G * c;
+        }
+        if (!found) return;
+    } else {
+        if (cta >= C) return;
+        u_begin = (long long)cta * U / C;
+        u_end = (long long)(cta + 1) * U / C;
+    }
+    if (warp == 0) TRACE(1);
 
     if (STAGED && warp == kWarps) {
         /* ================= producer warp: one lane streams the CTA's pages into the ring */
         if (lane == 0) {
             unsigned it = 0;
             bool ok = true;
+            bool waited = false;   /* griddepcontrol.wait executed yet? */
             for (long long u = u_begin; u < u_end && ok;) {
                 segment sg = locate(s_prefix, batch, n, G, u, u_end);
                 const int *bt = cache.block_table + (size_t)sg.seq * cache.max_blocks_per_seq;
@@ -460,14 +541,19 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     const unsigned stage = it % (unsigned)a.stages, phase = (it / (unsigned)a.stages) & 1u;
                     const int block = block_next;
                     if (p + 1 < sg.p_end) block_next = bt[p + 1];   /* in flight while we wait for the stage */
+                    /* before the preceding kernel is known to be complete only pages that lie wholly below
+                     * the newest slot may be fetched, and only into stages that were never used            */
+                    if (!waited && (it >= (unsigned)a.stages || (p + 1) * HY3A_PT > sg.len - 1)) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
                     ok = mbar_wait(bar_base + 64 + 8 * stage, phase ^ 1u, &s_abort, a.err, 1u);
                     if (!ok) break;
                     const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, sg.hl) * (size_t)cache.page_bytes;
                     mbar_expect_tx(bar_base + 8 * stage, (unsigned)geom.page_bytes);
                     bulk_g2s(ring_base + stage * (unsigned)geom.page_bytes, page, (unsigned)geom.page_bytes, bar_base + 8 * stage);
+                    TRACE(32 + it);
                 }
                 u = sg.seg_u0 + sg.p_end;
             }
+            if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
             if (!ok) {
                 /* gave up: let the copies already issued land before the CTA's shared memory goes away */
                 const unsigned first = it > (unsigned)a.stages ? it - (unsigned)a.stages : 0u;
@@ -481,7 +567,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     }
 
     /* ================= consumer warps */
-    int k_off[2][4];   /* [n-block][chunk], page-relative, loop invariant */
+    int k_off[2][4];   /* [n-block][chunk], relative to the granule, loop invariant */
     int v_off[8];
     int sc_off[2];
 #pragma unroll
@@ -510,46 +596,89 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             }
         }
     }
+    const unsigned sq = smem_u32(&s_q[0][lane]);
 
     unsigned it = 0; /* pages consumed by this CTA so far (ring position) */
     long long u = u_begin;
     while (u < u_end) {
         const segment sg = locate(s_prefix, batch, n, G, u, u_end);
         const int row = sg.row, hl = sg.hl, sidx = sg.sidx;
+        const float *qrow = a.q + (size_t)row * a.q_stride + (size_t)(cache.kv_head_begin + hl) * 8 * HY3A_D;
 
-        /* ---- Q operand fragments: fp16 value in rows 0-7, fp16 residual in rows 8-15.
-         * softmax scale 1/sqrt(128) (hy3_gpu.cu:193) and log2(e) are folded into Q.  Thread t < 256
-         * packs the entry of k-step t/32 for lane t%32; every warp then reads its lanes' entries. */
-        if (tid < 256) {
-            const int j = tid >> 5;
-            const float *qh = a.q + (size_t)row * a.q_stride + (size_t)((cache.kv_head_begin + hl) * 8 + g) * HY3A_D;
-            const float qs = 0.08838834764831845f * kLog2e;
-            float x[4], hi4[4], lo4[4];
+        /* ---- Q operand fragments of the segment's 8 heads, pre-packed per (k-step, lane).
+         * The softmax scale 1/sqrt(128) (hy3_gpu.cu:193) and log2(e) are folded in.          */
+        float qf = 1.f;
+        if (DT == 0) {
+            /* fp16 value in rows 0-7, fp16 residual in rows 8-15 */
+            if (tid < 256) {
+                const int j = tid >> 5;
+                const float *qh = qrow + g * HY3A_D;
+                const float qs = 0.08838834764831845f * kLog2e;
+                float x[4], hi4[4], lo4[4];
 #pragma unroll
-            for (int s = 0; s < 4; s++) x[s] = qh[kdim<DT>(j, tig, s)] * qs;
+                for (int s = 0; s < 4; s++) x[s] = qh[kdim16(j, tig, s)] * qs;
 #pragma unroll
-            for (int s = 0; s < 4; s++) { hi4[s] = __half2float(__float2half_rn(x[s])); lo4[s] = x[s] - hi4[s]; }
-            s_q[j][lane] = make_uint4(pack_h2(hi4[0], hi4[1]), pack_h2(lo4[0], lo4[1]), pack_h2(hi4[2], hi4[3]), pack_h2(lo4[2], lo4[3]));
+                for (int s = 0; s < 4; s++) { hi4[s] = __half2float(__float2half_rn(x[s])); lo4[s] = x[s] - hi4[s]; }
+                s_q[j][lane] = make_uint4(pack_h2(hi4[0], hi4[1]), pack_h2(lo4[0], lo4[1]), pack_h2(hi4[2], hi4[3]), pack_h2(lo4[2], lo4[3]));
+            }
+            consumer_sync();
+        } else {
+            /* two int8 digits per query element: q ~ sq*(hi + lo/254), |hi|,|lo| <= 127, so the
+             * quantisation step is absmax/32258 per head.  The digits are staged in the (idle)
+             * merge buffer, then packed into MMA A-fragments: rows 0-7 = hi, rows 8-15 = lo.     */
+            signed char *s_q8 = reinterpret_cast<signed char *>(s_dyn);   /* [2][8][128] */
+            if (warp < 8) {
+                const float4 xv = *reinterpret_cast<const float4 *>(qrow + warp * HY3A_D + 4 * lane);
+                const float x[4] = {xv.x, xv.y, xv.z, xv.w};
+                float m = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                const float sqv = m > 0.f ? m * (1.f / 127.f) : 1.f, inv = 1.f / sqv;
+                unsigned hw = 0, lw = 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float hi = fminf(127.f, fmaxf(-127.f, rintf(x[j] * inv)));
+                    const float lo = fminf(127.f, fmaxf(-127.f, rintf((x[j] - hi * sqv) * (254.f * inv))));
+                    hw |= ((unsigned)(int)hi & 0xFFu) << (8 * j);
+                    lw |= ((unsigned)(int)lo & 0xFFu) << (8 * j);
+                }
+                *reinterpret_cast<unsigned *>(s_q8 + warp * HY3A_D + 4 * lane) = hw;
+                *reinterpret_cast<unsigned *>(s_q8 + (8 + warp) * HY3A_D + 4 * lane) = lw;
+                if (lane == 0) s_qf[warp] = sqv * (1.f / 254.f) * 0.08838834764831845f * kLog2e * (DT == 2 ? 0.0625f : 1.f);
+            }
+            consumer_sync();
+            if (tid < 128) {
+                const int kk = tid >> 5;
+                unsigned w[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    const int d = kdim32<DT>(kk, tig, s);
+                    w[2 * (s >> 2)] |= ((unsigned)(unsigned char)s_q8[g * HY3A_D + d]) << (8 * (s & 3));
+                    w[2 * (s >> 2) + 1] |= ((unsigned)(unsigned char)s_q8[(8 + g) * HY3A_D + d]) << (8 * (s & 3));
+                }
+                s_q[kk][lane] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            consumer_sync();
+            qf = s_qf[g];
         }
-        consumer_sync();
-        const unsigned sq = smem_u32(&s_q[0][lane]);
-        /* P scale: w = p * vscale * 2^E with vs_max * 2^E <= 2^14, so fp16 P never
-         * overflows and its subnormal floor sits 2^-38 below the row maximum.          */
+        /* P scale: w = p * vscale * 2^E with vs_max * 2^E <= 2^6 and p <= 2^8, so fp16 P never
+         * overflows and its subnormal floor sits 2^-30 below the reference max.               */
         float pscale;
         {
-            int E = 14;
+            int E = 6;
             if (DT != 0) {
                 unsigned vb = cache.vs_max[a.layer * G + hl];
                 __half_raw hr; hr.x = (unsigned short)vb;
                 float vmax = __half2float(__half(hr));
                 int ex;
                 frexpf(fmaxf(vmax, 1e-30f), &ex); /* vmax < 2^ex */
-                E = 14 - ex;
+                E = 6 - ex;
                 E = E > 60 ? 60 : (E < -60 ? -60 : E);
             }
             pscale = exp2f((float)E);
         }
 
+        if (warp == 0) TRACE(2);
         warp_state st;
         st.m = -INFINITY; st.l = 0.f;
 #pragma unroll
@@ -565,20 +694,22 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             const int valid = min(HY3A_PT, sg.len - p * HY3A_PT);
             if (STAGED) {
                 const unsigned stage = pit % (unsigned)a.stages, phase = (pit / (unsigned)a.stages) & 1u;
+                const unsigned spage = ring_base + stage * (unsigned)geom.page_bytes;
                 mbar_wait(bar_base + 8 * stage, phase, &s_abort, a.err, 2u);
-                if (16 * gi < valid)
-                    granule<DT, true>(st, sq, nullptr, ring_base + stage * (unsigned)geom.page_bytes, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
+                if (16 * gi + 16 <= valid) granule<DT, true, true>(st, sq, qf, nullptr, spage, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
+                else if (16 * gi < valid) granule<DT, true, false>(st, sq, qf, nullptr, spage, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
                 mbar_arrive(bar_base + 64 + 8 * stage); /* every thread of the 8 warps that share a page releases it */
+                if (warp == 0) TRACE(3 + (x - it * 8u) / kWarps);
             } else {
                 if (16 * gi >= valid) continue; /* warp-uniform */
                 const int block = cache.block_table[(size_t)sg.seq * cache.max_blocks_per_seq + p];
                 const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, hl) * (size_t)cache.page_bytes;
-                granule<DT, false>(st, sq, page, 0u, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
+                granule<DT, false, false>(st, sq, qf, page, 0u, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
             }
         }
         it = it_end;
 
-        /* ---- fold the 8 warps of this CTA (shared memory) */
+        /* ---- fold the consumer warps of this CTA (shared memory) */
         {
             float l = st.l;
             l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -607,50 +738,68 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             float4 o4 = *reinterpret_cast<const float4 *>(&s_o[w][h][d4]);
             acc[0] += o4.x * f; acc[1] += o4.y * f; acc[2] += o4.z * f; acc[3] += o4.w * f;
         }
-        consumer_sync(); /* s_o / s_ml free for the next segment */
+        consumer_sync(); /* s_o / s_ml free again */
+        if (warp == 0) TRACE(24);
 
         /* ---- how many CTAs share this segment? */
-        const int c_first = (int)(((sg.seg_u0 + 1) * C + U - 1) / U) - 1;
-        const int c_last = (int)((sg.seg_u1 * C + U - 1) / U) - 1;
-        const int npieces = c_last - c_first + 1;
+        const int c_first = aligned ? al_first : (int)(((sg.seg_u0 + 1) * C + U - 1) / U) - 1;
+        const int npieces = aligned ? al_pieces : (int)((sg.seg_u1 * C + U - 1) / U) - 1 - c_first + 1;
+        const int rec_base = aligned ? 0 : sidx;   /* record index = CTA (+ segment when CTAs may hold several pieces) */
         const size_t head_q = (size_t)(cache.kv_head_begin + hl) * 8 + h; /* global query head */
         u = sg.seg_u0 + sg.p_end;
 
         if (npieces > 1) {
-            float *rec = a.scratch + ((size_t)(cta + sidx) * 8 + h) * HY3A_PARTIAL_FLOATS;
             if (red) {
+                float *rec = a.scratch + ((size_t)(cta + rec_base) * 8 + h) * HY3A_PARTIAL_FLOATS;
                 if (d4 == 0) { rec[0] = M; rec[1] = L; }
                 rec[2 + d4] = acc[0]; rec[3 + d4] = acc[1]; rec[4 + d4] = acc[2]; rec[5 + d4] = acc[3];
             }
-            __threadfence();
+            __threadfence();   /* every writer orders its part of the record before the arrival below */
             consumer_sync();
             if (tid == 0) {
                 unsigned old = atomicAdd(a.counters + sidx, 1u);
                 s_flag = (old == (unsigned)(npieces - 1));
             }
             consumer_sync();
-            if (!s_flag || !red) continue;
+            if (warp == 0) TRACE(25);
+            if (!s_flag) continue;   /* CTA-uniform */
             __threadfence();
-            /* last arrival: fold all pieces (hy3_gpu.cu:233-247 rule).  Two passes so that the
-             * loads of different pieces are independent and overlap: first the maxima, then the
-             * rescaled sums.  __ldcg reads L2, where the other CTAs' records are after their fence. */
-            M = -INFINITY;
-            for (int c = c_first; c <= c_last; c++) {
-                const float *pr = a.scratch + ((size_t)(c + sidx) * 8 + h) * HY3A_PARTIAL_FLOATS;
-                const float pm = __ldcg(pr), pl = __ldcg(pr + 1);
-                M = fmaxf(M, pl > 0.f ? pm : -INFINITY);
-            }
-            L = 0.f; acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-#pragma unroll 4
-            for (int c = c_first; c <= c_last; c++) {
-                const float *pr = a.scratch + ((size_t)(c + sidx) * 8 + h) * HY3A_PARTIAL_FLOATS;
-                const float pm = __ldcg(pr), pl = __ldcg(pr + 1);
-                const float2 a01 = __ldcg(reinterpret_cast<const float2 *>(pr + 2 + d4)), a23 = __ldcg(reinterpret_cast<const float2 *>(pr + 4 + d4));
-                const float rs = pl > 0.f ? ex2(pm - M) : 0.f;
-                L += pl * rs;
-                acc[0] += a01.x * rs; acc[1] += a01.y * rs; acc[2] += a23.x * rs; acc[3] += a23.y * rs;
+            /* last arrival: fold all pieces with the rule of hy3_gpu.cu:233-247.  The pieces' records
+             * (4160 contiguous bytes each) are fetched into shared memory with 16-byte asynchronous
+             * copies issued by all threads at once -- one L2 round trip for the whole segment instead
+             * of one per piece -- and folded from there.  Landing zone: the page ring when this CTA
+             * has no more pages to stream (always so when segments are CTA-aligned), else the merge
+             * buffer; larger segments go through it in several rounds.                              */
+            const bool ring_idle = STAGED && aligned;
+            const unsigned land = ring_idle ? ring_base : smem_u32(s_dyn);
+            const float *land_g = reinterpret_cast<const float *>(ring_idle ? s_dyn + kFixed + a.prefix_bytes + 128 : s_dyn);
+            const int land_cap = (ring_idle ? a.stages * geom.page_bytes : kFixedO) / (8 * HY3A_PARTIAL_FLOATS * 4);
+            M = -INFINITY; L = 0.f; acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            for (int c0 = 0; c0 < npieces; c0 += land_cap) {
+                const int nc = min(land_cap, npieces - c0);
+                const uint8_t *src = reinterpret_cast<const uint8_t *>(a.scratch + (size_t)(c_first + c0 + rec_base) * 8 * HY3A_PARTIAL_FLOATS);
+                for (int i = tid; i < nc * 260; i += kThreads)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(land + 16u * (unsigned)i), "l"(src + 16 * (size_t)i) : "memory");
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                consumer_sync();
+                if (red) {
+                    for (int c = 0; c < nc; c++) {
+                        const float *pr = land_g + ((size_t)c * 8 + h) * HY3A_PARTIAL_FLOATS;
+                        const float pm = pr[0], pl = pr[1];
+                        if (!(pl > 0.f)) continue;
+                        const float2 v01 = *reinterpret_cast<const float2 *>(pr + 2 + d4), v23 = *reinterpret_cast<const float2 *>(pr + 4 + d4);
+                        const float nm = fmaxf(M, pm), os = ex2(M - nm), rs = ex2(pm - nm);
+                        L = L * os + pl * rs;
+                        acc[0] = acc[0] * os + v01.x * rs; acc[1] = acc[1] * os + v01.y * rs;
+                        acc[2] = acc[2] * os + v23.x * rs; acc[3] = acc[3] * os + v23.y * rs;
+                        M = nm;
+                    }
+                }
+                if (c0 + land_cap < npieces) consumer_sync();   /* landing zone is reused */
             }
             if (tid == 0) a.counters[sidx] = 0u; /* self-reset for the next launch */
+            consumer_sync();   /* the landing zone is read; the next segment may reuse the buffer */
+            if (warp == 0) TRACE(26);
         }
         if (!red) continue;
         if (a.user_partials) {
@@ -700,7 +849,13 @@ static cudaError_t launch_decode_dt(hy3a_ctx *ctx, const hy3a_cache_view &cv, co
             if (e != cudaSuccess) return e;
             attr_set[DT][1] = true;
         }
-        hy3a_decode_kernel<DT, true><<<grid, kThreads + 32, smem, ctx->stream>>>(cv, bv, a);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = dim3(kThreads + 32); cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+        return cudaLaunchKernelEx(&cfg, hy3a_decode_kernel<DT, true>, cv, bv, a);
     } else {
         a.stages = 0;
         if (!attr_set[DT][0]) {
@@ -720,11 +875,14 @@ int hy3a_decode_ring_capacity(int page_bytes, int max_batch) {
     int s = room > 0 ? (int)(room / page_bytes) : 0;
     return s > 8 ? 8 : s;
 }
+/* Largest grid the last-arrival merge can stage in the merge buffer. */
+int hy3a_decode_max_ctas(void) { return kFixedO / 64; }
 
 int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride, float *partials) {
     decode_args a;
     a.q = q; a.q_stride = q_stride; a.out = out; a.out_stride = out_stride; a.user_partials = partials;
     a.scratch = ctx->d_partials; a.counters = ctx->d_counters; a.err = ctx->d_err; a.layer = layer;
+    a.trace = ctx->d_trace;
     hy3a_cache_view cv = hy3a_view(ctx);
     hy3a_batch_view bv = hy3a_bview(ctx);
     cudaError_t e;
@@ -735,6 +893,14 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
     }
     ctx->launches++;
     if (e != cudaSuccess) return hy3a_fail(ctx, HY3A_ECUDA, "decode launch: %s", cudaGetErrorString(e));
+    return HY3A_OK;
+}
+
+/* Development aid (trace builds): copy the per-CTA timestamps of the last decode launch to the host. */
+extern "C" int hy3a_debug_read_trace(hy3a_ctx *ctx, unsigned long long *out, int n_ctas) {
+    if (!ctx || !ctx->d_trace) return HY3A_EINVAL;
+    HY3A_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    HY3A_CUDA(ctx, cudaMemcpy(out, ctx->d_trace, (size_t)n_ctas * 64 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     return HY3A_OK;
 }
 

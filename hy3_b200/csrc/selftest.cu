@@ -114,7 +114,7 @@ done:
     hy3a_seq_release(ctx, 0, 0);
     ctx->batch_n = 0;
     /* the block the test used (the first one handed out) goes back zeroed */
-    cudaMemsetAsync(ctx->pool, 0, (size_t)ctx->cfg.n_layers * ctx->cfg.kv_head_count * ctx->geom.page_bytes, ctx->stream);
+    hy3a_launch_init_pages(ctx, 0, (size_t)ctx->cfg.n_layers * ctx->cfg.kv_head_count);
     cudaMemsetAsync(ctx->d_vs_max, 0, (size_t)ctx->cfg.n_layers * ctx->cfg.kv_head_count * sizeof(unsigned), ctx->stream);
     cudaStreamSynchronize(ctx->stream);
     ctx->launches = 0;
