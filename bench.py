@@ -204,14 +204,16 @@ def run_ours(args):
         """All launches of one step on `stream` (captured into a graph once)."""
         for l in range(n_layers):
             q, k, v = layer_views(l)
-            if owner:
-                ctx.append(l, q, k, v, q_out=qo[l])
+            if args.two_kernels:
+                ctx.append(l, q, k if owner else None, v if owner else None, q_out=qo[l])
+                if sharded is None:
+                    ctx.decode(l, qo[l], out=out[l])
+                else:
+                    sharded.step(l, qo[l], out[l])
+            elif sharded is None:
+                ctx.decode_step(l, q, k, v, out=out[l])        # fused norm+RoPE+quantise/append + attention
             else:
-                ctx.append(l, q, None, None, q_out=qo[l])   # only the rotated query is needed on this rank
-            if sharded is None:
-                ctx.decode(l, qo[l], out=out[l])
-            else:
-                sharded.step(l, qo[l], out[l])
+                sharded.step(l, (q, k if owner else None, v if owner else None), out[l])
 
     def set_positions(step):
         local_slot = ntok0 + step if owner else ntok0 - 1
@@ -348,6 +350,7 @@ def main():
     ap.add_argument("--ntok", type=int, default=NTOK)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--two-kernels", action="store_true", help="append and decode as separate launches instead of the fused step")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -42,8 +42,12 @@ class Hy3Attn:
             raise Hy3AttnError(rc, self.lib.hy3a_last_error(None).decode())
         self.h = h
         self.batch_n = 0
-        if stream is not None:
-            self.set_stream(stream)
+        if stream is None:
+            # work is enqueued on torch's current stream, so that it is ordered with the allocations,
+            # fills and copies torch does for the tensors handed to this object
+            import torch
+            stream = torch.cuda.current_stream(cfg.device if cfg.device >= 0 else None)
+        self.set_stream(stream)
 
     # ---- plumbing
     def _chk(self, rc):
@@ -144,6 +148,21 @@ class Hy3Attn:
             assert partials.is_contiguous() and partials.numel() == n * 8 * self.kv_head_count * PARTIAL_FLOATS
         self._chk(self.lib.hy3a_decode(self.h, layer, _ptr(q), q.stride(0), _ptr(out), 0 if out is None else out.stride(0),
                                        _ptr(partials)))
+        return out if partials is None else partials
+
+    def decode_step(self, layer, q, k, v, out=None, q_out=None, partials=None):
+        """Fused append + decode of one new token per batch row (pre-norm q [n,64,128], k/v [n,8,128])."""
+        import torch
+        n = self.batch_n
+        assert (k is None) == (v is None)
+        for t in (q, k, v):
+            assert t is None or (t.shape[0] == n and t.dtype == torch.float32 and t.stride(-1) == 1 and t.stride(-2) == D)
+        if partials is None and out is None:
+            out = torch.zeros((n, H, D), dtype=torch.float32, device=q.device)
+        self._chk(self.lib.hy3a_decode_step(self.h, layer, _ptr(q), q.stride(0), _ptr(k), 0 if k is None else k.stride(0),
+                                            _ptr(v), 0 if v is None else v.stride(0), _ptr(q_out),
+                                            0 if q_out is None else q_out.stride(0), _ptr(out),
+                                            0 if out is None else out.stride(0), _ptr(partials)))
         return out if partials is None else partials
 
     def merge_partials(self, partials, n_parts, n_rows, n_heads, out):

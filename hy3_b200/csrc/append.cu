@@ -23,61 +23,10 @@
 #include <math.h>
 
 #include "ctx.h"
+#include "rowops.cuh"
 
 namespace {
-
-__device__ __forceinline__ uint8_t *page_ptr(const hy3a_cache_view &c, int seq, int slot, int layer, int head_local) {
-    int block = c.block_table[(size_t)seq * c.max_blocks_per_seq + (slot >> 7)];
-    return c.pool + hy3a_page_index(c, block, layer, head_local) * (size_t)c.page_bytes;
-}
-
-/* Quantise (or round to fp16) the warp's 128 values y[4] (dims d0..d0+3 per lane) and
- * store them as row `tok` (0..127) of the page.  is_v selects the V area / pair layout.
- * Returns the fp16 scale bits (0 for FP16 caches).                                    */
-template <int DT>
-__device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g, int tok, bool is_v, const float y[4], int d0, int lane) {
-    if (DT == 0) {
-        __half2 h01 = __floats2half2_rn(y[0], y[1]);
-        __half2 h23 = __floats2half2_rn(y[2], y[3]);
-        uint2 w;
-        w.x = *reinterpret_cast<unsigned *>(&h01);
-        w.y = *reinterpret_cast<unsigned *>(&h23);
-        int off = is_v ? g.v_off + hy3a_v16_dim_off(tok, d0) : hy3a_k_dim_off<0>(tok, d0);
-        *reinterpret_cast<uint2 *>(page + off) = w;
-        return 0u;
-    }
-    float m = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const float qmax = (DT == 1) ? 127.f : 7.f;
-    float s = __fadd_rn(__fdiv_rn(m, qmax), 1e-8f);
-    float inv = __fdiv_rn(1.f, s);
-    int c[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) c[j] = (int)roundf(fmaxf(-qmax, fminf(qmax, __fmul_rn(y[j], inv))));
-    __half sh = __float2half(s);
-    unsigned sbits = (unsigned)__half_as_ushort(sh);
-    if (lane == 0) *reinterpret_cast<unsigned short *>(page + (is_v ? g.vs_off : g.ks_off) + tok * 2) = (unsigned short)sbits;
-    if (DT == 1) {
-        if (!is_v) {
-            unsigned w = (unsigned)(c[0] & 0xFF) | ((unsigned)(c[1] & 0xFF) << 8) | ((unsigned)(c[2] & 0xFF) << 16) | ((unsigned)(c[3] & 0xFF) << 24);
-            *reinterpret_cast<unsigned *>(page + hy3a_k_dim_off<1>(tok, d0)) = w;
-        } else {
-            /* V codes are kept offset-binary (c + 128): the decode kernel's byte-permute conversion
-             * to fp16 then needs no sign fix-up; export converts back to two's complement          */
-            unsigned short u0 = (unsigned short)((((c[0] & 0xFF) | ((c[1] & 0xFF) << 8))) ^ 0x8080);
-            unsigned short u1 = (unsigned short)((((c[2] & 0xFF) | ((c[3] & 0xFF) << 8))) ^ 0x8080);
-            *reinterpret_cast<unsigned short *>(page + g.v_off + hy3a_v_unit_off<1>(tok, d0)) = u0;
-            *reinterpret_cast<unsigned short *>(page + g.v_off + hy3a_v_unit_off<1>(tok, d0 + 2)) = u1;
-        }
-    } else {
-        unsigned short u = (unsigned short)((c[0] & 0xF) | ((c[1] & 0xF) << 4) | ((c[2] & 0xF) << 8) | ((c[3] & 0xF) << 12));
-        if (is_v) u ^= 0x8888;   /* V nibbles offset-binary (n + 8), as for INT8 */
-        int off = is_v ? g.v_off + hy3a_v_unit_off<2>(tok, d0) : hy3a_k_dim_off<2>(tok, d0);
-        *reinterpret_cast<unsigned short *>(page + off) = u;
-    }
-    return sbits;
-}
+using namespace hy3a_rowops;
 
 struct append_args {
     const float *q_in, *k_in, *v_in;
@@ -93,10 +42,10 @@ struct append_args {
 /* grid (10, n_rows), block 256: warp (blockIdx.x*8 + warp) in [0,80) = 64 Q, 8 K, 8 V heads. */
 template <int DT>
 __global__ void __launch_bounds__(256) hy3a_append_kernel(hy3a_cache_view cache, hy3a_batch_view batch, hy3a_rope_params rope, append_args a) {
-    /* programmatic dependent launch: let the next kernel start its prologue, then wait until the
-     * preceding kernel's results are complete (no-ops without the launch attribute)             */
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    /* programmatic dependent launch: wait until the preceding kernel's results are complete, then
+     * let the next kernel start its prologue (no-ops without the launch attribute)              */
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int row = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hr = blockIdx.x * 8 + warp;
@@ -114,34 +63,7 @@ __global__ void __launch_bounds__(256) hy3a_append_kernel(hy3a_cache_view cache,
     float4 xv = *reinterpret_cast<const float4 *>(src + (size_t)head * HY3A_D + d0);
     float y[4] = {xv.x, xv.y, xv.z, xv.w};
 
-    if (is_q || is_k) {
-        /* sum of squares, reference tree order */
-        float sq[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) sq[j] = __fmul_rn(y[j], y[j]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-            for (int j = 0; j < 4; j++) sq[j] = __fadd_rn(sq[j], __shfl_xor_sync(0xffffffffu, sq[j], o));
-        }
-        float ss = __fadd_rn(__fadd_rn(sq[0], sq[2]), __fadd_rn(sq[1], sq[3]));
-        float r = rsqrtf(ss / (float)HY3A_D + a.eps);
-        const float *w = a.norm_w + (is_k ? HY3A_D : 0);
-        float4 wv = *reinterpret_cast<const float4 *>(w + d0);
-        y[0] = y[0] * r * wv.x; y[1] = y[1] * r * wv.y; y[2] = y[2] * r * wv.z; y[3] = y[3] * r * wv.w;
-        /* RoPE */
-        int pos = (ti + (ti >= rope.pos_jump_at ? rope.pos_jump : 0)) * rope.pos_stride;
-        float4 fv = *reinterpret_cast<const float4 *>(rope.inv_freq + idx * 4);
-        float fr4[4] = {fv.x, fv.y, fv.z, fv.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            float other = __shfl_xor_sync(0xffffffffu, y[j], 16);
-            float fr = (float)pos * fr4[j];
-            float c = cosf(fr) * rope.attn_factor, s = sinf(fr) * rope.attn_factor;
-            float v0 = half ? other : y[j], v1 = half ? y[j] : other;
-            y[j] = half ? (v1 * c + v0 * s) : (v0 * c - v1 * s);
-        }
-    }
+    if (is_q || is_k) norm_rope_row(y, a.norm_w + (is_k ? HY3A_D : 0), a.eps, rope, ti, lane);
     if (is_q) {
         if (a.q_out) *reinterpret_cast<float4 *>(a.q_out + (size_t)row * a.q_out_stride + (size_t)head * HY3A_D + d0) = make_float4(y[0], y[1], y[2], y[3]);
         if (a.q_out16) {
@@ -285,12 +207,14 @@ int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_str
         default: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<2>, cv, bv, ctx->rope, a); break;
     }
     ctx->launches++;
+    if (ctx->batch_n > 1) ctx->bulk_write_pending = 1;
     HY3A_CUDA(ctx, e);
     return HY3A_OK;
 }
 
 int hy3a_launch_fill_random(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint64_t seed) {
     hy3a_cache_view cv = hy3a_view(ctx);
+    ctx->bulk_write_pending = 1;
     for (int done = 0; done < n;) {
         int chunk = n - done > 32768 ? 32768 : n - done;
         dim3 grid(2, chunk), block(256);
@@ -308,6 +232,7 @@ int hy3a_launch_fill_random(hy3a_ctx *ctx, int layer, int seq, int t0, int n, ui
 
 int hy3a_launch_export(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint8_t *d_kslots, uint8_t *d_vslots, int import) {
     hy3a_cache_view cv = hy3a_view(ctx);
+    if (import) ctx->bulk_write_pending = 1;
     long long total = (long long)n * 8 * 32 * 2;
     int block = 256;
     unsigned grid = (unsigned)((total + block - 1) / block);

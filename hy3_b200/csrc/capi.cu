@@ -378,7 +378,28 @@ int hy3a_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float
     if (!q || (!out && !partials)) return hy3a_fail(ctx, HY3A_EINVAL, "decode: NULL argument");
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)partials) & 15) return hy3a_fail(ctx, HY3A_EINVAL, "decode: pointers must be 16-byte aligned");
     if ((q_stride | out_stride) & 3) return hy3a_fail(ctx, HY3A_EINVAL, "decode: strides must be multiples of 4 floats");
-    return hy3a_launch_decode(ctx, layer, q, q_stride, out, out_stride, partials);
+    return hy3a_launch_decode(ctx, layer, q, q_stride, out, out_stride, partials, NULL);
+}
+
+int hy3a_decode_step(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, const float *k_in, size_t k_stride, const float *v_in,
+                     size_t v_stride, float *q_out, size_t q_out_stride, float *out, size_t out_stride, float *partials) {
+    int rc = check_layer(ctx, layer, "decode_step");
+    if (rc) return rc;
+    if (!q_in || (!k_in) != (!v_in) || (!out && !partials)) return hy3a_fail(ctx, HY3A_EINVAL, "decode_step: NULL argument");
+    if (((uintptr_t)q_in | (uintptr_t)k_in | (uintptr_t)v_in | (uintptr_t)q_out | (uintptr_t)out | (uintptr_t)partials) & 15)
+        return hy3a_fail(ctx, HY3A_EINVAL, "decode_step: pointers must be 16-byte aligned");
+    if ((q_stride | k_stride | v_stride | q_out_stride | out_stride) & 3) return hy3a_fail(ctx, HY3A_EINVAL, "decode_step: strides must be multiples of 4 floats");
+    if (ctx->decode_stages < 2) {
+        /* no shared-memory ring (tuning knob): run the two kernels one after the other */
+        if (!q_out) return hy3a_fail(ctx, HY3A_EINVAL, "decode_step: q_out is required when the page ring is disabled");
+        rc = hy3a_launch_append(ctx, layer, q_in, q_stride, k_in, k_stride, v_in, v_stride, q_out, q_out_stride, NULL);
+        if (rc) return rc;
+        return hy3a_launch_decode(ctx, layer, q_out, q_out_stride, out, out_stride, partials, NULL);
+    }
+    hy3a_step_inputs st;
+    st.q_in = q_in; st.k_in = k_in; st.v_in = v_in; st.q_stride = q_stride; st.k_stride = k_stride; st.v_stride = v_stride;
+    st.q_out = q_out; st.q_out_stride = q_out_stride;
+    return hy3a_launch_decode(ctx, layer, NULL, 0, out, out_stride, partials, &st);
 }
 
 int hy3a_merge_partials(hy3a_ctx *ctx, const float *partials, int n_parts, int n_rows, int n_heads, float *out, size_t out_stride) {

@@ -82,6 +82,7 @@ struct hy3a_ctx {
     unsigned int *h_err;  /* pinned */
     int batch_n;
     int decode_ctas;
+    int bulk_write_pending; /* a kernel that wrote many KV slots was enqueued and no decode launch has followed it yet */
     int use_pdl;          /* launch kernels with programmatic stream serialization (HY3A_NO_PDL=1 turns it off) */
     int decode_stages;    /* pages in the decode kernel's shared-memory ring; < 2 selects the direct-load variant */
 
@@ -93,8 +94,15 @@ struct hy3a_ctx {
 /* internal kernel launchers (defined in the .cu files) */
 int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, const float *k_in, size_t k_stride,
                        const float *v_in, size_t v_stride, float *q_out, size_t q_out_stride, void *q_out16);
+/* inputs of the fused step (pre-norm rows of the new token per batch row); NULL = plain decode */
+struct hy3a_step_inputs {
+    const float *q_in, *k_in, *v_in;
+    size_t q_stride, k_stride, v_stride;
+    float *q_out;
+    size_t q_out_stride;
+};
 int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride,
-                       float *partials);
+                       float *partials, const hy3a_step_inputs *step);
 int hy3a_launch_merge(hy3a_ctx *ctx, const float *partials, int n_parts, int n_rows, int n_heads, float *out,
                       size_t out_stride);
 int hy3a_launch_export(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint8_t *d_kslots, uint8_t *d_vslots, int import);

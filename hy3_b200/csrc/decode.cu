@@ -37,8 +37,10 @@
  */
 #include <cuda_fp16.h>
 #include <math.h>
+#include <string.h>
 
 #include "ctx.h"
+#include "rowops.cuh"
 
 namespace {
 
@@ -160,6 +162,17 @@ struct decode_args {
     unsigned int *counters;
     unsigned int *err;
     int layer;
+    /* fused step (fused != 0): the kernel itself normalises + rotates the queries read from q_in and
+     * the CTA that streams the page of the newest slot quantises and appends the new K / V row   */
+    int fused;
+    int early_prefetch;   /* pages below the newest slots may be fetched before griddepcontrol.wait */
+    const float *q_in, *k_in, *v_in;
+    size_t qi_stride, ki_stride, vi_stride;
+    float *q_out;         /* optional: normalised + rotated queries, fp32 [n][64][128] */
+    size_t q_out_stride;
+    const float *norm_w;  /* [2][128] of this layer */
+    float eps;
+    hy3a_rope_params rope;
     int stages;           /* staged variant: pages in the shared-memory ring (2..8) */
     int prefix_bytes;     /* bytes reserved for the page-count prefix */
 };
@@ -417,6 +430,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     float (*s_ml)[8][2] = reinterpret_cast<float (*)[8][2]>(s_dyn + kFixedO);                      /* per-warp {m, l} */
     uint4 (*s_q)[32] = reinterpret_cast<uint4 (*)[32]>(s_dyn + kFixedO + kFixedML);                /* Q fragments: [k-step][lane] */
     __shared__ float s_qf[8];
+    __shared__ unsigned s_vnew;
     __shared__ int s_flag;
     __shared__ int s_abort;
 
@@ -426,9 +440,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     const int n = batch.n, G = cache.kv_heads;
     const int cta = blockIdx.x;
     if (warp == 0) TRACE(0);
-    /* Programmatic dependent launch: the next kernel in the stream may begin its own prologue now.
-     * (No-ops when the launch does not carry the attribute.)                                        */
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     int *s_prefix = reinterpret_cast<int *>(s_dyn + kFixed);
     const unsigned bar_base = smem_u32(s_dyn + kFixed + a.prefix_bytes);
     const unsigned ring_base = bar_base + 128;
@@ -464,28 +476,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     __syncthreads();
 
     const long long U = (long long)G * s_prefix[n];
-    /* Everything above reads only what the host wrote (batch descriptor).  From here on the kernel
-     * touches memory that the preceding kernel in the stream may produce (queries, the newest KV
-     * slot, scratch records), so wait for it -- except the producer lane, which first starts the
-     * copies of pages that lie wholly below the newest slot (append-only cache: immutable).       */
-    const bool is_producer = STAGED && warp == kWarps;
-    if (!is_producer) asm volatile("griddepcontrol.wait;" ::: "memory");
-    /* rows with no keys on this rank: zero output / empty partial (hy3_gpu.cu:197-199) */
-    for (int i = cta; i < n; i += gridDim.x) {
-        if (s_prefix[i + 1] != s_prefix[i]) continue;
-        for (int e = tid; e < G * 8 * HY3A_D && !is_producer; e += kThreads) {
-            int hq = e / HY3A_D, d = e % HY3A_D;
-            if (a.user_partials) {
-                float *p = a.user_partials + ((size_t)i * G * 8 + hq) * HY3A_PARTIAL_FLOATS;
-                p[2 + d] = 0.f;
-                if (d == 0) { p[0] = -INFINITY; p[1] = 0.f; }
-            } else {
-                a.out[(size_t)i * a.out_stride + (size_t)(cache.kv_head_begin * 8 + hq) * HY3A_D + d] = 0.f;
-            }
-        }
-    }
-
-    if (U == 0) return;
+    bool idle = (U == 0);
     /* Two ways to cut the units into per-CTA ranges:
      *  - few segments (n*G < grid): every segment gets its own whole number of CTAs, roughly in
      *    proportion to its pages, so no CTA straddles two segments (a straddling CTA pays the
@@ -494,9 +485,10 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
      * In both, never more CTAs than units, and the CTAs sharing a segment are contiguous.       */
     const bool aligned = (long long)n * G < (long long)gridDim.x;
     int C = (long long)gridDim.x < U ? (int)gridDim.x : (int)U;
-    long long u_begin, u_end;
+    long long u_begin = 0, u_end = 0;
     int al_first = 0, al_pieces = 1;
-    if (aligned) {
+    if (idle) {
+    } else if (aligned) {
         int rows_ne = 0;
         for (int r = 0; r < n; r++) rows_ne += (s_prefix[r + 1] != s_prefix[r]);
         const long long spare = (long long)gridDim.x - (long long)rows_ne * G, P = s_prefix[n];
@@ -519,12 +511,54 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             }
             base += G * c;
         }
-        if (!found) return;
+        if (!found) idle = true;
     } else {
-        if (cta >= C) return;
+        if (cta >= C) idle = true;
         u_begin = (long long)cta * U / C;
         u_end = (long long)(cta + 1) * U / C;
+        if (idle) u_begin = u_end = 0;
     }
+    /* ---- fused step, still before the wait: what the query set-up needs besides the queries themselves
+     * (norm weights, RoPE table, the row's position -> cos/sin) comes from the host, so warps 0-7 fetch
+     * and compute it now, off the critical path.                                                       */
+    const int rl_d0 = (lane >> 4) * 64 + (lane & 15) * 4;
+    float4 pre_w = make_float4(1.f, 1.f, 1.f, 1.f);
+    float pre_c[4] = {1.f, 1.f, 1.f, 1.f}, pre_s[4] = {0.f, 0.f, 0.f, 0.f};
+    int pre_row = -1;
+    if (a.fused && !idle && warp < 8) {
+        pre_w = *reinterpret_cast<const float4 *>(a.norm_w + rl_d0);
+        pre_row = locate(s_prefix, batch, n, G, u_begin, u_end).row;
+        hy3a_rowops::rope_coeffs(pre_c, pre_s, a.rope, batch.pos[pre_row], lane);
+    }
+    /* Everything above reads only what the host wrote (batch descriptor).  From here on the kernel
+     * touches memory that the preceding kernel in the stream may produce (queries, the newest KV
+     * slot, scratch records), so wait for it -- except the producer lane, which first starts the
+     * copies of pages that lie wholly below the newest slot (append-only cache: immutable).       */
+    const bool is_producer = STAGED && warp == kWarps;
+    if (!is_producer) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        /* Only now may the NEXT kernel in the stream start its prologue: it then knows that everything
+         * older than this kernel is complete, so the only writes it can race with are this kernel's
+         * (the newest slot of each row), which its early page fetches stay clear of.                  */
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+    /* rows with no keys on this rank: zero output / empty partial (hy3_gpu.cu:197-199) */
+    for (int i = cta; i < n; i += gridDim.x) {
+        if (s_prefix[i + 1] != s_prefix[i]) continue;
+        for (int e = tid; e < G * 8 * HY3A_D && !is_producer; e += kThreads) {
+            int hq = e / HY3A_D, d = e % HY3A_D;
+            if (a.user_partials) {
+                float *p = a.user_partials + ((size_t)i * G * 8 + hq) * HY3A_PARTIAL_FLOATS;
+                p[2 + d] = 0.f;
+                if (d == 0) { p[0] = -INFINITY; p[1] = 0.f; }
+            } else {
+                a.out[(size_t)i * a.out_stride + (size_t)(cache.kv_head_begin * 8 + hq) * HY3A_D + d] = 0.f;
+            }
+        }
+    }
+
+    if (idle) return;
+
     if (warp == 0) TRACE(1);
 
     if (STAGED && warp == kWarps) {
@@ -533,6 +567,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             unsigned it = 0;
             bool ok = true;
             bool waited = false;   /* griddepcontrol.wait executed yet? */
+            if (!a.early_prefetch) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
             for (long long u = u_begin; u < u_end && ok;) {
                 segment sg = locate(s_prefix, batch, n, G, u, u_end);
                 const int *bt = cache.block_table + (size_t)sg.seq * cache.max_blocks_per_seq;
@@ -543,7 +578,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     if (p + 1 < sg.p_end) block_next = bt[p + 1];   /* in flight while we wait for the stage */
                     /* before the preceding kernel is known to be complete only pages that lie wholly below
                      * the newest slot may be fetched, and only into stages that were never used            */
-                    if (!waited && (it >= (unsigned)a.stages || (p + 1) * HY3A_PT > sg.len - 1)) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+                    if (!waited && (it >= (unsigned)a.stages || (p + 1) * HY3A_PT > sg.len - 2)) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
                     ok = mbar_wait(bar_base + 64 + 8 * stage, phase ^ 1u, &s_abort, a.err, 1u);
                     if (!ok) break;
                     const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, sg.hl) * (size_t)cache.page_bytes;
@@ -603,33 +638,35 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     while (u < u_end) {
         const segment sg = locate(s_prefix, batch, n, G, u, u_end);
         const int row = sg.row, hl = sg.hl, sidx = sg.sidx;
-        const float *qrow = a.q + (size_t)row * a.q_stride + (size_t)(cache.kv_head_begin + hl) * 8 * HY3A_D;
+        const int head0 = (cache.kv_head_begin + hl) * 8;   /* first of the segment's 8 query heads */
 
         /* ---- Q operand fragments of the segment's 8 heads, pre-packed per (k-step, lane).
-         * The softmax scale 1/sqrt(128) (hy3_gpu.cu:193) and log2(e) are folded in.          */
+         * Warp w < 8 owns head w as a row of 4 values per lane (dims d0..d0+3); in the fused step it
+         * first applies the per-head RMSNorm and RoPE (same code as the append kernel).  The softmax
+         * scale 1/sqrt(128) (hy3_gpu.cu:193) and log2(e) are folded into the fragments.            */
         float qf = 1.f;
-        if (DT == 0) {
-            /* fp16 value in rows 0-7, fp16 residual in rows 8-15 */
-            if (tid < 256) {
-                const int j = tid >> 5;
-                const float *qh = qrow + g * HY3A_D;
-                const float qs = 0.08838834764831845f * kLog2e;
-                float x[4], hi4[4], lo4[4];
-#pragma unroll
-                for (int s = 0; s < 4; s++) x[s] = qh[kdim16(j, tig, s)] * qs;
-#pragma unroll
-                for (int s = 0; s < 4; s++) { hi4[s] = __half2float(__float2half_rn(x[s])); lo4[s] = x[s] - hi4[s]; }
-                s_q[j][lane] = make_uint4(pack_h2(hi4[0], hi4[1]), pack_h2(lo4[0], lo4[1]), pack_h2(hi4[2], hi4[3]), pack_h2(lo4[2], lo4[3]));
+        float *s_qx = reinterpret_cast<float *>(s_dyn);                 /* FP16 cache: [8][128] fp32 staging */
+        signed char *s_q8 = reinterpret_cast<signed char *>(s_dyn);     /* INT8/INT4: [2][8][128] int8 digits */
+        if (warp < 8) {
+            const int d0 = (lane >> 4) * 64 + (lane & 15) * 4;
+            float x[4];
+            if (a.fused) {
+                const float4 xv = *reinterpret_cast<const float4 *>(a.q_in + (size_t)row * a.qi_stride + (size_t)(head0 + warp) * HY3A_D + d0);
+                x[0] = xv.x; x[1] = xv.y; x[2] = xv.z; x[3] = xv.w;
+                if (row != pre_row) { hy3a_rowops::rope_coeffs(pre_c, pre_s, a.rope, batch.pos[row], lane); pre_row = row; }
+                hy3a_rowops::norm_rope_apply(x, pre_w, a.eps, pre_c, pre_s, lane);
+                if (a.q_out && sg.p_begin == 0)
+                    *reinterpret_cast<float4 *>(a.q_out + (size_t)row * a.q_out_stride + (size_t)(head0 + warp) * HY3A_D + d0) = make_float4(x[0], x[1], x[2], x[3]);
+            } else {
+                const float4 xv = *reinterpret_cast<const float4 *>(a.q + (size_t)row * a.q_stride + (size_t)(head0 + warp) * HY3A_D + d0);
+                x[0] = xv.x; x[1] = xv.y; x[2] = xv.z; x[3] = xv.w;
             }
-            consumer_sync();
-        } else {
-            /* two int8 digits per query element: q ~ sq*(hi + lo/254), |hi|,|lo| <= 127, so the
-             * quantisation step is absmax/32258 per head.  The digits are staged in the (idle)
-             * merge buffer, then packed into MMA A-fragments: rows 0-7 = hi, rows 8-15 = lo.     */
-            signed char *s_q8 = reinterpret_cast<signed char *>(s_dyn);   /* [2][8][128] */
-            if (warp < 8) {
-                const float4 xv = *reinterpret_cast<const float4 *>(qrow + warp * HY3A_D + 4 * lane);
-                const float x[4] = {xv.x, xv.y, xv.z, xv.w};
+            if (DT == 0) {
+                const float qs = 0.08838834764831845f * kLog2e;
+                *reinterpret_cast<float4 *>(s_qx + warp * HY3A_D + d0) = make_float4(x[0] * qs, x[1] * qs, x[2] * qs, x[3] * qs);
+            } else {
+                /* two int8 digits per query element: q ~ sq*(hi + lo/254), |hi|,|lo| <= 127, so the
+                 * quantisation step is absmax/32258 per head                                       */
                 float m = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -642,25 +679,52 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     hw |= ((unsigned)(int)hi & 0xFFu) << (8 * j);
                     lw |= ((unsigned)(int)lo & 0xFFu) << (8 * j);
                 }
-                *reinterpret_cast<unsigned *>(s_q8 + warp * HY3A_D + 4 * lane) = hw;
-                *reinterpret_cast<unsigned *>(s_q8 + (8 + warp) * HY3A_D + 4 * lane) = lw;
+                *reinterpret_cast<unsigned *>(s_q8 + warp * HY3A_D + d0) = hw;
+                *reinterpret_cast<unsigned *>(s_q8 + (8 + warp) * HY3A_D + d0) = lw;
                 if (lane == 0) s_qf[warp] = sqv * (1.f / 254.f) * 0.08838834764831845f * kLog2e * (DT == 2 ? 0.0625f : 1.f);
             }
-            consumer_sync();
+        } else if (warp == 8) {
+            /* fused step: the scale the new V row will get (hy3_gpu.cu:260-262), so that every CTA of the
+             * segment sizes its P scale for it as well                                                 */
+            unsigned vb = 0;
+            if (DT != 0 && a.fused && a.k_in) {
+                const float4 xv = *reinterpret_cast<const float4 *>(a.v_in + (size_t)row * a.vi_stride + (size_t)(cache.kv_head_begin + hl) * HY3A_D + 4 * lane);
+                float m = fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w)));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                vb = (unsigned)__half_as_ushort(__float2half(__fadd_rn(__fdiv_rn(m, DT == 1 ? 127.f : 7.f), 1e-8f)));
+            }
+            if (lane == 0) s_vnew = vb;
+        }
+        consumer_sync();
+        if (DT == 0) {
+            /* fp16 value in rows 0-7, fp16 residual in rows 8-15 */
+            if (tid < 256) {
+                const int j = tid >> 5;
+                float xx[4], hi4[4], lo4[4];
+#pragma unroll
+                for (int s2 = 0; s2 < 4; s2++) xx[s2] = s_qx[g * HY3A_D + kdim16(j, tig, s2)];
+#pragma unroll
+                for (int s2 = 0; s2 < 4; s2++) { hi4[s2] = __half2float(__float2half_rn(xx[s2])); lo4[s2] = xx[s2] - hi4[s2]; }
+                s_q[j][lane] = make_uint4(pack_h2(hi4[0], hi4[1]), pack_h2(lo4[0], lo4[1]), pack_h2(hi4[2], hi4[3]), pack_h2(lo4[2], lo4[3]));
+            }
+        } else {
+            /* pack the digits into MMA A-fragments: rows 0-7 = hi, rows 8-15 = lo */
             if (tid < 128) {
                 const int kk = tid >> 5;
                 unsigned w[4] = {0, 0, 0, 0};
 #pragma unroll
-                for (int s = 0; s < 8; s++) {
-                    const int d = kdim32<DT>(kk, tig, s);
-                    w[2 * (s >> 2)] |= ((unsigned)(unsigned char)s_q8[g * HY3A_D + d]) << (8 * (s & 3));
-                    w[2 * (s >> 2) + 1] |= ((unsigned)(unsigned char)s_q8[(8 + g) * HY3A_D + d]) << (8 * (s & 3));
+                for (int s2 = 0; s2 < 8; s2++) {
+                    const int d = kdim32<DT>(kk, tig, s2);
+                    w[2 * (s2 >> 2)] |= ((unsigned)(unsigned char)s_q8[g * HY3A_D + d]) << (8 * (s2 & 3));
+                    w[2 * (s2 >> 2) + 1] |= ((unsigned)(unsigned char)s_q8[(8 + g) * HY3A_D + d]) << (8 * (s2 & 3));
                 }
                 s_q[kk][lane] = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            consumer_sync();
             qf = s_qf[g];
         }
+        const unsigned vnew = s_vnew;
+        consumer_sync();
         /* P scale: w = p * vscale * 2^E with vs_max * 2^E <= 2^6 and p <= 2^8, so fp16 P never
          * overflows and its subnormal floor sits 2^-30 below the reference max.               */
         float pscale;
@@ -668,6 +732,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             int E = 6;
             if (DT != 0) {
                 unsigned vb = cache.vs_max[a.layer * G + hl];
+                vb = vb > vnew ? vb : vnew;   /* positive fp16 bit patterns order like the numbers */
                 __half_raw hr; hr.x = (unsigned short)vb;
                 float vmax = __half2float(__half(hr));
                 int ex;
@@ -696,6 +761,28 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 const unsigned stage = pit % (unsigned)a.stages, phase = (pit / (unsigned)a.stages) & 1u;
                 const unsigned spage = ring_base + stage * (unsigned)geom.page_bytes;
                 mbar_wait(bar_base + 8 * stage, phase, &s_abort, a.err, 2u);
+                if (a.fused && a.k_in && p == ((sg.len - 1) >> 7) && gi == (((sg.len - 1) & 127) >> 4)) {
+                    /* fused append: this warp holds the only granule that contains the newest slot.  It
+                     * normalises, rotates and quantises the new K row and quantises the new V row exactly
+                     * as the append kernel does, writes them to the page in HBM (for later steps) and into
+                     * the shared-memory copy it is about to read.                                         */
+                    const int d0 = (lane >> 4) * 64 + (lane & 15) * 4, tok = (sg.len - 1) & 127;
+                    const int block = cache.block_table[(size_t)sg.seq * cache.max_blocks_per_seq + p];
+                    uint8_t *gp = cache.pool + hy3a_page_index(cache, block, a.layer, hl) * (size_t)cache.page_bytes;
+                    uint8_t *sp = s_dyn + kFixed + a.prefix_bytes + 128 + (size_t)stage * geom.page_bytes;
+                    const int kvh = cache.kv_head_begin + hl;
+                    float4 kv4 = *reinterpret_cast<const float4 *>(a.k_in + (size_t)row * a.ki_stride + (size_t)kvh * HY3A_D + d0);
+                    float y[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
+                    hy3a_rowops::norm_rope_row(y, a.norm_w + HY3A_D, a.eps, a.rope, batch.pos[row], lane);
+                    hy3a_rowops::store_row<DT>(gp, geom, tok, false, y, d0, lane);
+                    hy3a_rowops::store_row<DT>(sp, geom, tok, false, y, d0, lane);
+                    kv4 = *reinterpret_cast<const float4 *>(a.v_in + (size_t)row * a.vi_stride + (size_t)kvh * HY3A_D + d0);
+                    y[0] = kv4.x; y[1] = kv4.y; y[2] = kv4.z; y[3] = kv4.w;
+                    const unsigned sb = hy3a_rowops::store_row<DT>(gp, geom, tok, true, y, d0, lane);
+                    hy3a_rowops::store_row<DT>(sp, geom, tok, true, y, d0, lane);
+                    if (DT != 0 && lane == 0) atomicMax(cache.vs_max + a.layer * G + hl, sb);
+                    __syncwarp();
+                }
                 if (16 * gi + 16 <= valid) granule<DT, true, true>(st, sq, qf, nullptr, spage, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
                 else if (16 * gi < valid) granule<DT, true, false>(st, sq, qf, nullptr, spage, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
                 mbar_arrive(bar_base + 64 + 8 * stage); /* every thread of the 8 warps that share a page releases it */
@@ -878,11 +965,21 @@ int hy3a_decode_ring_capacity(int page_bytes, int max_batch) {
 /* Largest grid the last-arrival merge can stage in the merge buffer. */
 int hy3a_decode_max_ctas(void) { return kFixedO / 64; }
 
-int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride, float *partials) {
+int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride, float *partials,
+                       const hy3a_step_inputs *step) {
     decode_args a;
+    memset(&a, 0, sizeof(a));
     a.q = q; a.q_stride = q_stride; a.out = out; a.out_stride = out_stride; a.user_partials = partials;
     a.scratch = ctx->d_partials; a.counters = ctx->d_counters; a.err = ctx->d_err; a.layer = layer;
     a.trace = ctx->d_trace;
+    a.early_prefetch = ctx->use_pdl && !ctx->bulk_write_pending;
+    if (step) {
+        a.fused = 1;
+        a.q_in = step->q_in; a.k_in = step->k_in; a.v_in = step->v_in;
+        a.qi_stride = step->q_stride; a.ki_stride = step->k_stride; a.vi_stride = step->v_stride;
+        a.q_out = step->q_out; a.q_out_stride = step->q_out_stride;
+        a.norm_w = ctx->d_norm_w + (size_t)layer * 2 * HY3A_D; a.eps = ctx->cfg.rms_eps; a.rope = ctx->rope;
+    }
     hy3a_cache_view cv = hy3a_view(ctx);
     hy3a_batch_view bv = hy3a_bview(ctx);
     cudaError_t e;
@@ -892,6 +989,7 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
         default: e = launch_decode_dt<2>(ctx, cv, bv, a); break;
     }
     ctx->launches++;
+    ctx->bulk_write_pending = 0;   /* the kernel after this one only has this one to stay clear of */
     if (e != cudaSuccess) return hy3a_fail(ctx, HY3A_ECUDA, "decode launch: %s", cudaGetErrorString(e));
     return HY3A_OK;
 }

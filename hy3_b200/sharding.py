@@ -67,7 +67,10 @@ def make_cuda_sharded_decode(ctx, n_rows, group=None):
     n_heads = 8 * ctx.kv_head_count
 
     def partial_fn(layer, q, buf):
-        ctx.decode(layer, q, partials=buf)
+        if isinstance(q, tuple):            # (q_in, k_in, v_in): fused step on pre-norm rows
+            ctx.decode_step(layer, q[0], q[1], q[2], partials=buf)
+        else:
+            ctx.decode(layer, q, partials=buf)
 
     def merge_fn(gathered, n_parts, out):
         ctx.merge_partials(gathered, n_parts, n_rows, n_heads, out)

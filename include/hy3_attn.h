@@ -140,6 +140,19 @@ int hy3a_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, co
 int hy3a_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride,
                 float *partials);
 
+/* The decode step as ONE kernel: hy3a_append (for one new token per batch row) fused into
+ * hy3a_decode.  Replaces the four launches per layer of the reference's decode loop --
+ * qk_norm_rope_fused_kernel, kv_quantize_*, attention_split_kv_*, attention_reduce_kernel
+ * (hy3_gpu.cu:750-758).  q_in/k_in/v_in: pre-norm fp32 rows of the new token as for
+ * hy3a_append (k_in and v_in may both be NULL: nothing is appended, see there); q_out
+ * (optional): the normalised + rotated queries; out / partials as for hy3a_decode.  Each
+ * CTA normalises and rotates the 8 queries of its KV head itself; the one CTA that streams
+ * the page holding the newest slot quantises and stores the new K / V row (bit-identical to
+ * hy3a_append) and attends over it from shared memory.                                   */
+int hy3a_decode_step(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, const float *k_in, size_t k_stride,
+                     const float *v_in, size_t v_stride, float *q_out, size_t q_out_stride, float *out, size_t out_stride,
+                     float *partials);
+
 /* Merge n_parts partial records per head in index order with the online-softmax rule of
  * attention_reduce_kernel (hy3_gpu.cu:233-247).  partials: [n_parts][n_rows*n_heads][130]
  * (the layout an all-gather of hy3a_decode partials produces), out: [n_rows][out_stride]

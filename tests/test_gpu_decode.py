@@ -136,6 +136,51 @@ def test_append_then_decode_end_to_end(cuda, oracle):
     ctx.close()
 
 
+@pytest.mark.parametrize("dt", ["int8", "int4", "fp16"])
+def test_fused_step_equals_append_plus_decode(cuda, oracle, dt):
+    """hy3a_decode_step (one kernel) against hy3a_append + hy3a_decode: identical cache bytes, identical
+    queries, identical outputs; a ragged batch so that page and granule boundaries are crossed."""
+    import torch
+    from hy3_b200 import Hy3Attn
+    lens0 = [0, 15, 16, 127, 128, 300, 2000]          # tokens already cached per sequence
+    B, steps = len(lens0), 18
+    w = (1.0 + 0.02 * oracle.fill_normal((2, 128), SEED, 3)).astype(np.float32)
+    q = oracle.fill_normal((steps, B, 64, 128), SEED, 401)
+    k = oracle.fill_normal((steps, B, 8, 128), SEED, 402)
+    v = oracle.fill_normal((steps, B, 8, 128), SEED, 403)
+    res = {}
+    for mode in ("two_kernels", "fused"):
+        ctx = Hy3Attn(kv_dtype=dt, n_layers=2, max_seqs=B, max_batch=B, max_tokens=4096 + 128 * B, max_tokens_per_seq=2560, rms_eps=1e-6)
+        ctx.set_norm_weights(1, w[0], w[1])
+        for s_, n0 in enumerate(lens0):
+            if n0:
+                ctx.fill_random(1, s_, 0, n0, 77)
+        outs, qos = [], []
+        tq, tk, tv = (torch.from_numpy(a).to(cuda) for a in (q, k, v))
+        for t in range(steps):
+            ctx.batch_set(list(range(B)), [n0 + t for n0 in lens0], [n0 + t + 5 for n0 in lens0])
+            if mode == "fused":
+                qo = torch.zeros((B, 64, 128), dtype=torch.float32, device=cuda)
+                out = ctx.decode_step(1, tq[t], tk[t], tv[t], q_out=qo)
+            else:
+                qo = ctx.append(1, tq[t], tk[t], tv[t])
+                out = ctx.decode(1, qo)
+            outs.append(out); qos.append(qo)
+        ctx.sync()
+        caches = [ctx.export_kv(1, s_, 0, n0 + steps) for s_, n0 in enumerate(lens0)]
+        res[mode] = (torch.stack(outs).cpu().numpy(), torch.stack(qos).cpu().numpy(), caches)
+        if mode == "fused":        # and against the oracle on the stored cache, last step
+            for s_ in (0, 3, 6):
+                Kf = slots_to_float(oracle, caches[s_][0], dt); Vf = slots_to_float(oracle, caches[s_][1], dt)
+                check_attention(res[mode][0][-1, s_], oracle.attention(res[mode][1][-1, s_], Kf, Vf), "fused %s seq %d" % (dt, s_))
+        ctx.close()
+    a, b = res["two_kernels"], res["fused"]
+    assert np.array_equal(a[1], b[1]), "queries differ"
+    for (ka, va), (kb, vb) in zip(a[2], b[2]):
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb), "cache bytes differ"
+    assert np.array_equal(a[0], b[0]), "outputs differ: max %.3g" % np.abs(a[0] - b[0]).max()
+
+
 def test_partials_and_merge_sequence_shards(cuda, oracle):
     """Two contexts hold the two halves of one sequence; per-shard {m,l,acc} + merge == full attention."""
     import torch
