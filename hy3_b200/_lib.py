@@ -44,6 +44,7 @@ PROTOTYPES = {
     "hy3a_append": (_i, [_vp, _i, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp]),
     "hy3a_decode": (_i, [_vp, _i, _vp, _sz, _vp, _sz, _vp]),
     "hy3a_decode_step": (_i, [_vp, _i, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp]),
+    "hy3a_decode_noalloc": (_i, [_vp, _i, _vp, _sz, _vp, _sz]),
     "hy3a_merge_partials": (_i, [_vp, _vp, _i, _i, _i, _vp, _sz]),
     "hy3a_prefill": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _sz]),
     "hy3a_export_kv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp]),

@@ -994,6 +994,64 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
     return HY3A_OK;
 }
 
+/* ---- decode without any allocation ---------------------------------------------------------
+ * Scratch for hy3a_decode_noalloc: the records and arrival counters of the cross-CTA merge live in
+ * this file-scope device array instead of buffers the context allocated.  Every GPU that loads the
+ * library holds these 2.6 MB until the process exits.  Layout: [kNoAllocRecords][8][130] floats of
+ * records, then kNoAllocCounters arrival counters.                                               */
+constexpr int kNoAllocRows = 64;                                   /* most (batch row, KV head) segments per call */
+constexpr int kNoAllocRecords = 512 + kNoAllocRows;                /* one per CTA of the largest grid + one per segment */
+constexpr size_t kNoAllocRecordBytes = (size_t)kNoAllocRecords * 8 * HY3A_PARTIAL_FLOATS * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocRecordBytes + kNoAllocRows * sizeof(unsigned)];
+static unsigned char *g_noalloc_ptr[64];                           /* device address of the array, per device ordinal */
+
+extern "C" int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride) {
+    if (!ctx) return HY3A_EINVAL;
+    if (layer < 0 || layer >= ctx->cfg.n_layers) return hy3a_fail(ctx, HY3A_EINVAL, "decode_noalloc: layer %d out of range", layer);
+    if (ctx->batch_n < 1) return hy3a_fail(ctx, HY3A_ESTATE, "decode_noalloc: no batch set (call hy3a_batch_set first)");
+    if (!q || !out || (((uintptr_t)q | (uintptr_t)out) & 15) || ((q_stride | out_stride) & 3))
+        return hy3a_fail(ctx, HY3A_EINVAL, "decode_noalloc: q and out must be non-NULL, 16-byte aligned, strides multiples of 4");
+    if (ctx->batch_n * ctx->cfg.kv_head_count > kNoAllocRows)
+        return hy3a_fail(ctx, HY3A_EINVAL, "decode_noalloc: %d batch rows x %d KV heads exceed the built-in scratch (%d segments); use hy3a_decode",
+                         ctx->batch_n, ctx->cfg.kv_head_count, kNoAllocRows);
+    if (ctx->decode_ctas > 512) return hy3a_fail(ctx, HY3A_EINVAL, "decode_noalloc: grid of %d CTAs exceeds the built-in scratch", ctx->decode_ctas);
+    if (ctx->device < 0 || ctx->device >= 64) return hy3a_fail(ctx, HY3A_EINVAL, "decode_noalloc: device ordinal %d not supported", ctx->device);
+    if (!g_noalloc_ptr[ctx->device]) {
+        /* one-time set-up on this device: in host code the array's name is only a handle, the kernel
+         * needs the device address                                                                 */
+        int cur = -1;
+        HY3A_CUDA(ctx, cudaGetDevice(&cur));
+        if (cur != ctx->device) HY3A_CUDA(ctx, cudaSetDevice(ctx->device));
+        void *p = NULL;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (cur != ctx->device) cudaSetDevice(cur);
+        if (e != cudaSuccess || !p) return hy3a_fail(ctx, HY3A_ECUDA, "decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_noalloc_ptr[ctx->device] = (unsigned char *)p;
+    }
+    unsigned char *scratch = g_noalloc_ptr[ctx->device];
+    /* the arrival counters must start at zero; a call that was cut short may have left some behind */
+    HY3A_CUDA(ctx, cudaMemsetAsync(scratch + kNoAllocRecordBytes, 0, kNoAllocRows * sizeof(unsigned), ctx->stream));
+    decode_args a;
+    memset(&a, 0, sizeof(a));
+    a.q = q; a.q_stride = q_stride; a.out = out; a.out_stride = out_stride;
+    a.scratch = reinterpret_cast<float *>(scratch);
+    a.counters = reinterpret_cast<unsigned *>(scratch + kNoAllocRecordBytes);
+    a.err = ctx->d_err; a.layer = layer; a.trace = ctx->d_trace;
+    a.early_prefetch = 0;
+    hy3a_cache_view cv = hy3a_view(ctx);
+    hy3a_batch_view bv = hy3a_bview(ctx);
+    cudaError_t e;
+    switch (ctx->cfg.kv_dtype) {
+        case 0: e = launch_decode_dt<0>(ctx, cv, bv, a); break;
+        case 1: e = launch_decode_dt<1>(ctx, cv, bv, a); break;
+        default: e = launch_decode_dt<2>(ctx, cv, bv, a); break;
+    }
+    ctx->launches++;
+    ctx->bulk_write_pending = 0;
+    if (e != cudaSuccess) return hy3a_fail(ctx, HY3A_ECUDA, "decode_noalloc launch: %s", cudaGetErrorString(e));
+    return HY3A_OK;
+}
+
 /* Development aid (trace builds): copy the per-CTA timestamps of the last decode launch to the host. */
 extern "C" int hy3a_debug_read_trace(hy3a_ctx *ctx, unsigned long long *out, int n_ctas) {
     if (!ctx || !ctx->d_trace) return HY3A_EINVAL;

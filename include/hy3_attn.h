@@ -153,6 +153,25 @@ int hy3a_decode_step(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_strid
                      const float *v_in, size_t v_stride, float *q_out, size_t q_out_stride, float *out, size_t out_stride,
                      float *partials);
 
+/* hy3a_decode for callers that must not allocate.  (No counterpart in the reference: this entry
+ * point exists only in this library.)  Some callers cannot tolerate a device allocation on the
+ * decode path -- code that runs while the rest of the process has the allocator locked or has
+ * handed all free memory to another pool, or that may not take the implicit device-wide
+ * synchronisation an allocation or free can cause.  hy3a_decode itself never allocates either,
+ * but it leans on scratch buffers that hy3a_create allocated; this variant keeps the scratch of
+ * the cross-CTA merge (the {m, l, acc} records and their arrival counters) in a fixed array that
+ * is part of the library image, so it works on a context whatever happened to those buffers and
+ * never calls cudaMalloc, cudaFree or any allocating routine.  Same arguments and results as
+ * hy3a_decode without `partials`.
+ * Limits: at most 64 (batch row, owned KV head) pairs per call, i.e. 8 rows with all 8 KV heads;
+ * larger batches are refused with HY3A_EINVAL.  The array (2.6 MB) is held by every GPU that
+ * loads the library until the process exits.  The first call on a device looks the array's
+ * device address up (cudaGetSymbolAddress) -- make that first call outside any stream capture.
+ * All contexts on a device share the array, and it keeps the last call's contents (the counters
+ * are cleared at each call): calls that can overlap on the GPU -- different streams, or different
+ * contexts -- race with each other; serialise them.                                          */
+int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride);
+
 /* Merge n_parts partial records per head in index order with the online-softmax rule of
  * attention_reduce_kernel (hy3_gpu.cu:233-247).  partials: [n_parts][n_rows*n_heads][130]
  * (the layout an all-gather of hy3a_decode partials produces), out: [n_rows][out_stride]
