@@ -1,5 +1,469 @@
-/* prefill.cu -- placeholder until the tcgen05 kernel lands. */
+/*
+ * prefill.cu -- causal chunk attention on 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+ *
+ * Replaces prefill_attn_int8/int4_kernel (hy3_gpu.cu:383-447), which walks the keys serially with
+ * one warp per (query head, 16-query tile) on CUDA cores.  Semantics kept: query i of the chunk has
+ * global index base+i and attends keys [0, base+i]; the chunk's own K/V were appended first, so
+ * queries see the cache's (quantised) K/V also for their own chunk (hy3_gpu.cu:823-832).
+ *
+ * Two kernels per (layer, chunk):
+ *   1. hy3a_kv_to_f16_kernel<DT>: gathers the sequence's pages of this layer into a dense fp16
+ *      workspace, dequantising INT8/INT4 (value = code * fp16 scale, hy3_gpu.cu:206-215): K as
+ *      [head][token][128] (d contiguous) and V TRANSPOSED as [head][128][token] (tokens contiguous),
+ *      so that both are K-major operands for the tensor cores.
+ *   2. hy3a_prefill_kernel: one CTA per (16 query tokens x the 8 query heads of one KV head) = a
+ *      128-row Q tile (GQA packing: the 8 heads share every K/V tile).  Warp-specialised:
+ *        warp 4   TMA producer: Q once, then K_j / V_j tiles (128 keys) into 2-stage rings
+ *                 (cp.async.bulk.tensor, 128-byte swizzle, mbarrier transaction counts)
+ *        warp 5   MMA issuer (one elected lane): S_j = Q.K_j^T and O += P_j.V_j with
+ *                 tcgen05.mma.cta_group::1.kind::f16, M=128 N=128 K=16, accumulators in TMEM
+ *                 (S double-buffered: columns 0-127 / 128-255, O: columns 256-383);
+ *                 tcgen05.commit signals mbarriers
+ *        warps 0-3  softmax, one thread per row: tcgen05.ld the row of S, online softmax in base 2
+ *                 with a lazily updated reference max, P_j as fp16 into shared memory in the
+ *                 tensor core's swizzled K-major layout, conditional rescale of O in TMEM
+ *                 (tcgen05.ld / tcgen05.st); epilogue O / l -> fp32 output.
+ *      Causal masking only touches the tiles that cross the diagonal.
+ *
+ * Every wait is bounded; a wait that runs out raises a CTA-wide abort flag, records a code in the
+ * context's error word, lets all warps fall through to the end, and TMEM is always released.
+ *
+ * Roofline: tensor (dense fp16).  Algorithmic FLOPs = 4 * 128 * 64 * sum over queries of (pos+1).
+ */
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
 #include "ctx.h"
-int hy3a_launch_prefill(hy3a_ctx *ctx, int, int, int, int, const void *, float *, size_t) {
-    return hy3a_fail(ctx, HY3A_ESTATE, "prefill: kernel not built into this library");
+
+namespace {
+
+constexpr int kQTok = 16;            /* query tokens per CTA (x 8 heads = 128 rows) */
+constexpr int kKeys = 128;           /* keys per K/V tile */
+constexpr int kTileBytes = 128 * 128 * 2;   /* one 128x128 fp16 operand tile = two 16 KB swizzled sub-tiles */
+constexpr int kPfThreads = 192;
+/* shared memory map (bytes from a 1024-aligned base) */
+constexpr int kOffQ = 0, kOffK = kOffQ + kTileBytes, kOffV = kOffK + 2 * kTileBytes, kOffP = kOffV + 2 * kTileBytes;
+constexpr int kOffBar = kOffP + kTileBytes;          /* 16 mbarriers + tmem address + abort flag */
+constexpr int kPfSmem = kOffBar + 256 + 1024;        /* + slack for the 1024-byte alignment */
+enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_P = 13, BAR_O = 14 };
+constexpr float kScaleLog2 = 0.08838834764831845f * 1.4426950408889634f;   /* 1/sqrt(128) * log2(e) */
+constexpr float kPfThreshold = 8.f;
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(unsigned bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+__device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+/* bounded wait, see the header comment */
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, unsigned *err, unsigned where) {
+    if (mbar_test(bar, parity)) return true;
+    for (unsigned i = 0; i < (1u << 22); i++) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 63u) == 63u) { if (*abort_flag) return false; __nanosleep(32); }
+    }
+    *abort_flag = 1;
+    if (atomicCAS(err, 0u, 2u) == 0u) err[1] = where;
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap *map, unsigned bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+/* shared-memory matrix descriptor: K-major, 128-byte swizzle; 8-row groups 1024 B apart (SBO), LBO = 1 (unused
+ * for swizzled K-major), descriptor version 1 (Blackwell), layout type 2 = SWIZZLE_128B                       */
+__device__ __forceinline__ unsigned long long make_desc(unsigned saddr) {
+    return (unsigned long long)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+/* instruction descriptor: D = f32 (bit 4), A = B = f16 (0), both K-major, N = 128 (>>3 at bit 17), M = 128 (>>4 at bit 24) */
+constexpr unsigned kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+__device__ __forceinline__ void umma_f16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ float ex2f(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+__device__ __forceinline__ unsigned pack_h2(float lo, float hi) { unsigned r; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+
+/* ---- pass 1: pages -> dense fp16 K [head][tok][128] and V^T [head][128][tok] ------------------- */
+template <int DT>
+__global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cache, int layer, int seq, int ntok, int tok_stride, __half *ws_k, __half *ws_vt) {
+    const hy3a_geom g = hy3a_make_geom(DT);
+    const int pg = blockIdx.x, hl = blockIdx.y, tid = threadIdx.x;
+    const int block = cache.block_table[(size_t)seq * cache.max_blocks_per_seq + pg];
+    const uint8_t *page = cache.pool + hy3a_page_index(cache, block, layer, hl) * (size_t)cache.page_bytes;
+    const __half *ks = reinterpret_cast<const __half *>(page + g.ks_off), *vs = reinterpret_cast<const __half *>(page + g.vs_off);
+    /* K: 128 tokens x 16 groups of 8 dims */
+    for (int idx = tid; idx < 128 * 16; idx += 256) {
+        const int tok = idx >> 4, d = (idx & 15) * 8, t = pg * 128 + tok;
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (t < ntok) {
+            if (DT == 0) {
+                o = *reinterpret_cast<const uint4 *>(page + hy3a_k_dim_off<0>(tok, d));
+            } else {
+                const float s = __half2float(ks[tok]);
+                float f[8];
+                if (DT == 1) {
+                    const uint2 w = *reinterpret_cast<const uint2 *>(page + hy3a_k_dim_off<1>(tok, d));
+                    const unsigned ww[2] = {w.x, w.y};
+#pragma unroll
+                    for (int i = 0; i < 8; i++) f[i] = (float)(signed char)((ww[i >> 2] >> (8 * (i & 3))) & 0xFF) * s;
+                } else {
+                    const unsigned w = *reinterpret_cast<const unsigned *>(page + hy3a_k_dim_off<2>(tok, d));
+#pragma unroll
+                    for (int i = 0; i < 8; i++) { int n = (w >> (4 * i)) & 0xF; f[i] = (float)(n > 7 ? n - 16 : n) * s; }
+                }
+                __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]), h2 = __floats2half2_rn(f[4], f[5]), h3 = __floats2half2_rn(f[6], f[7]);
+                o = make_uint4(*reinterpret_cast<unsigned *>(&h0), *reinterpret_cast<unsigned *>(&h1), *reinterpret_cast<unsigned *>(&h2), *reinterpret_cast<unsigned *>(&h3));
+            }
+        }
+        *reinterpret_cast<uint4 *>(ws_k + ((size_t)hl * tok_stride + t) * HY3A_D + d) = o;
+    }
+    /* V^T: thread = (dim, half of the page's tokens); 8 consecutive tokens per 16-byte store */
+    const int d = tid & 127, th = tid >> 7;
+    for (int t8 = 0; t8 < 8; t8++) {
+        __half hv[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int tok = th * 64 + t8 * 8 + i, t = pg * 128 + tok;
+            float v = 0.f;
+            if (t < ntok) {
+                if (DT == 0) {
+                    v = __half2float(*reinterpret_cast<const __half *>(page + g.v_off + hy3a_v16_dim_off(tok, d)));
+                } else if (DT == 1) {
+                    const int b = page[g.v_off + hy3a_v_unit_off<1>(tok, d & ~1) + (d & 1)];
+                    v = (float)(b - 128) * __half2float(vs[tok]);
+                } else {
+                    const int b = page[g.v_off + hy3a_v_unit_off<2>(tok, d & ~3) + ((d & 3) >> 1)];
+                    v = (float)(((b >> ((d & 1) * 4)) & 0xF) - 8) * __half2float(vs[tok]);
+                }
+            }
+            hv[i] = __float2half_rn(v);
+        }
+        *reinterpret_cast<uint4 *>(ws_vt + ((size_t)hl * HY3A_D + d) * tok_stride + pg * 128 + th * 64 + t8 * 8) = *reinterpret_cast<uint4 *>(hv);
+    }
+}
+
+struct prefill_args {
+    float *out;
+    size_t out_stride;
+    int base, nq, kv_head_begin;
+    unsigned *err;
+};
+
+/* ---- pass 2: the attention kernel -------------------------------------------------------------- */
+__global__ void __launch_bounds__(kPfThreads, 1)
+hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
+    extern __shared__ uint8_t s_raw[];
+    uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~(uintptr_t)1023);
+    const unsigned sbase = smem_u32(sm);
+    const unsigned bar0 = sbase + kOffBar;
+    volatile unsigned *s_tmem = reinterpret_cast<volatile unsigned *>(sm + kOffBar + 128);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kOffBar + 132);
+#define BAR(i) (bar0 + 8u * (unsigned)(i))
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q0 = blockIdx.x * kQTok, hl = blockIdx.y;
+    const int kv_end = min(a.base + q0 + kQTok, a.base + a.nq);   /* keys [0, kv_end) matter for this tile */
+    const int ntiles = (kv_end + kKeys - 1) / kKeys;
+
+    if (tid == 0) {
+        *s_abort = 0;
+        mbar_init(BAR(BAR_Q), 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(BAR(BAR_KF + i), 1); mbar_init(BAR(BAR_VF + i), 1); mbar_init(BAR(BAR_KE + i), 1); mbar_init(BAR(BAR_VE + i), 1);
+            mbar_init(BAR(BAR_SF + i), 1); mbar_init(BAR(BAR_SE + i), 128);
+        }
+        mbar_init(BAR(BAR_P), 128);
+        mbar_init(BAR(BAR_O), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {   /* one warp allocates all 512 TMEM columns (1 CTA per SM) */
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + kOffBar + 128), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = *s_tmem;
+    const unsigned tm_s[2] = {tmem, tmem + 128u}, tm_o = tmem + 256u;
+
+    if (warp == 4) {
+        /* ===================== TMA producer ===================== */
+        if (lane == 0) {
+            mbar_expect_tx(BAR(BAR_Q), kTileBytes);
+            tma_load_3d(sbase + kOffQ, &tm_q, BAR(BAR_Q), 0, (a.kv_head_begin + hl) * 8, q0);
+            tma_load_3d(sbase + kOffQ + 16384, &tm_q, BAR(BAR_Q), 64, (a.kv_head_begin + hl) * 8, q0);
+            for (int j = 0; j < ntiles; j++) {
+                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
+                if (!mbar_wait(BAR(BAR_KE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
+                mbar_expect_tx(BAR(BAR_KF + st), kTileBytes);
+                tma_load_3d(sbase + kOffK + st * kTileBytes, &tm_k, BAR(BAR_KF + st), 0, j * kKeys, hl);
+                tma_load_3d(sbase + kOffK + st * kTileBytes + 16384, &tm_k, BAR(BAR_KF + st), 64, j * kKeys, hl);
+                if (!mbar_wait(BAR(BAR_VE + st), ph ^ 1u, s_abort, a.err, 11u)) break;
+                mbar_expect_tx(BAR(BAR_VF + st), kTileBytes);
+                tma_load_3d(sbase + kOffV + st * kTileBytes, &tm_v, BAR(BAR_VF + st), j * kKeys, 0, hl);
+                tma_load_3d(sbase + kOffV + st * kTileBytes + 16384, &tm_v, BAR(BAR_VF + st), j * kKeys + 64, 0, hl);
+            }
+        }
+    } else if (warp == 5) {
+        /* ===================== MMA issuer ===================== */
+        if (lane == 0) {
+            bool ok = mbar_wait(BAR(BAR_Q), 0u, s_abort, a.err, 20u);
+            /* S_j = Q . K_j^T : 8 k-steps of 16 over d = 128 (two swizzled 64-wide sub-tiles) */
+            auto issue_qk = [&](int j) {
+                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
+                if (!mbar_wait(BAR(BAR_KF + st), ph, s_abort, a.err, 21u)) return false;
+                if (!mbar_wait(BAR(BAR_SE + st), ph ^ 1u, s_abort, a.err, 22u)) return false;   /* S buffer read out by the softmax warps */
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    const unsigned off = (unsigned)(kk >> 2) * 16384u + (unsigned)(kk & 3) * 32u;
+                    umma_f16(tm_s[st], make_desc(sbase + kOffQ + off), make_desc(sbase + kOffK + st * kTileBytes + off), kk > 0);
+                }
+                umma_commit(BAR(BAR_SF + st));   /* S_j ready */
+                umma_commit(BAR(BAR_KE + st));   /* K stage free */
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < ntiles && ok; j++) {
+                if (j + 1 < ntiles) ok = issue_qk(j + 1);
+                if (!ok) break;
+                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
+                if (!mbar_wait(BAR(BAR_VF + st), ph, s_abort, a.err, 23u)) break;
+                if (!mbar_wait(BAR(BAR_P), (unsigned)j & 1u, s_abort, a.err, 24u)) break;       /* P_j written (and O rescaled) */
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                /* O += P_j . V_j : 8 k-steps of 16 over the 128 keys */
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    const unsigned off = (unsigned)(kk >> 2) * 16384u + (unsigned)(kk & 3) * 32u;
+                    umma_f16(tm_o, make_desc(sbase + kOffP + off), make_desc(sbase + kOffV + st * kTileBytes + off), (j > 0 || kk > 0));
+                }
+                umma_commit(BAR(BAR_O));          /* O updated, P buffer free */
+                umma_commit(BAR(BAR_VE + st));    /* V stage free */
+            }
+        }
+    } else {
+        /* ===================== softmax warps 0-3: thread = row of the Q tile ===================== */
+        const int r = tid, t_local = r >> 3, h = r & 7;
+        const int qpos = a.base + q0 + t_local;                 /* global index of this row's query */
+        const bool row_valid = (q0 + t_local) < a.nq;
+        const unsigned lane_base = (unsigned)(warp * 32) << 16; /* this warp's quarter of the TMEM lanes */
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; j++) {
+            const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(BAR(BAR_SF + st), ph, s_abort, a.err, 30u));   /* keep the warp together */
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int k0 = j * kKeys;
+            const bool masked = (k0 + kKeys - 1 > a.base + q0);   /* the tile crosses the diagonal of some row */
+            /* pass 1: row max */
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                unsigned v[32];
+                tmem_ld32(tm_s[st] + lane_base + 32u * c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float s = __uint_as_float(v[i]) * kScaleLog2;
+                    if (masked && k0 + 32 * c + i > qpos) s = -INFINITY;
+                    mx = fmaxf(mx, s);
+                }
+            }
+            const bool grow = mx > m + kPfThreshold;              /* true while m == -inf (key 0 is never masked) */
+            const float m_new = grow ? mx : m;
+            /* pass 2: P = 2^(s - m) as fp16 pairs, l from the rounded values */
+            unsigned pk[64];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                unsigned v[32];
+                tmem_ld32(tm_s[st] + lane_base + 32u * c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float s0 = __uint_as_float(v[i]) * kScaleLog2, s1 = __uint_as_float(v[i + 1]) * kScaleLog2;
+                    if (masked && k0 + 32 * c + i > qpos) s0 = -INFINITY;
+                    if (masked && k0 + 32 * c + i + 1 > qpos) s1 = -INFINITY;
+                    const unsigned p2 = pack_h2(ex2f(s0 - m_new), ex2f(s1 - m_new));
+                    pk[16 * c + (i >> 1)] = p2;
+                }
+            }
+            /* S_j is in registers: hand the buffer back to the tensor core */
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(BAR(BAR_SE + st));
+            float lsum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 64; i++) { const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&pk[i])); lsum += f.x + f.y; }
+            /* O and the P buffer are only ours again when P_{j-1}.V_{j-1} has completed */
+            if (j > 0 && ok) {
+                ok = __all_sync(0xffffffffu, mbar_wait(BAR(BAR_O), (unsigned)(j - 1) & 1u, s_abort, a.err, 31u));
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            /* tcgen05.ld / .st are warp-collective: the whole warp rescales its 32 rows as soon as one of them
+             * moved its reference (the others multiply by exactly 1)                                          */
+            const float alpha = grow ? ex2f(m - m_new) : 1.f;     /* 0 on the first tile (m = -inf) */
+            if (__any_sync(0xffffffffu, grow)) {
+                l *= alpha;
+                if (j > 0) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        unsigned v[32];
+                        tmem_ld32(tm_o + lane_base + 32u * c, v);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tmem_st32(tm_o + lane_base + 32u * c, v);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                m = m_new;
+            }
+            l += lsum;
+            /* P row r into the swizzled K-major layout: 16-byte chunk c of sub-tile c/8 lands at chunk (c%8)^(r%8) */
+            {
+                uint8_t *prow = sm + kOffP + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+                for (int c = 0; c < 16; c++) {
+                    uint4 w = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                    *reinterpret_cast<uint4 *>(prow + (c >> 3) * 16384 + (((c & 7) ^ (r & 7)) << 4)) = w;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   /* generic-proxy writes -> visible to the tensor core */
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(BAR(BAR_P));
+        }
+        /* epilogue: O / l */
+        if (ok && ntiles > 0) ok = mbar_wait(BAR(BAR_O), (unsigned)(ntiles - 1) & 1u, s_abort, a.err, 32u);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__all_sync(0xffffffffu, ok) && ntiles > 0) {      /* warp-uniform: tcgen05.ld is warp-collective */
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float *orow = a.out + (size_t)(q0 + t_local) * a.out_stride + (size_t)((a.kv_head_begin + hl) * 8 + h) * HY3A_D;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                unsigned v[32];
+                tmem_ld32(tm_o + lane_base + 32u * c, v);
+                if (row_valid)
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4 *>(orow + 32 * c + i) = make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
+                                                                                   __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            }
+        }
+    }
+    /* ---- common exit: everybody arrives here, also after a wait ran out; release TMEM */
+    if (*s_abort && warp == 4 && lane == 0) {
+        /* copies already issued must land before the shared memory goes away */
+        for (int st = 0; st < 2; st++)
+            for (unsigned ph = 0; ph < 2; ph++)
+                for (unsigned spin = 0; spin < (1u << 12) && !mbar_test(BAR(BAR_KF + st), ph) && !mbar_test(BAR(BAR_VF + st), ph); spin++) __nanosleep(64);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+#undef BAR
+}
+
+} /* namespace */
+
+typedef CUresult (*hy3a_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                         const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                         CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static hy3a_encode_tiled_fn get_encode_tiled(void) {
+    static hy3a_encode_tiled_fn fn = NULL;
+    if (!fn) {
+        void *p = NULL;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = (hy3a_encode_tiled_fn)p;
+    }
+    return fn;
+}
+
+/* 3-D fp16 tensor map with a 128-byte swizzle; dims/box innermost first, strides in bytes for dims 1 and 2 */
+static int make_map(hy3a_ctx *ctx, CUtensorMap *map, void *base, const cuuint64_t dims[3], const cuuint64_t strides[2], const cuuint32_t box[3]) {
+    hy3a_encode_tiled_fn enc = get_encode_tiled();
+    if (!enc) return hy3a_fail(ctx, HY3A_ECUDA, "prefill: cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return hy3a_fail(ctx, HY3A_ECUDA, "prefill: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return HY3A_OK;
+}
+
+int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq, const void *q16, float *out, size_t out_stride) {
+    const int kvh = ctx->cfg.kv_head_count;
+    const int ntok = base_slot + nq;
+    const int pages = (ntok + HY3A_PT - 1) / HY3A_PT;
+    const int tok_stride = pages * HY3A_PT;
+    /* fp16 workspace for this layer's K and V^T (grow-only, in steps of 1024 tokens) */
+    const size_t need = (size_t)kvh * (((size_t)tok_stride + 1023) / 1024 * 1024) * HY3A_D * sizeof(__half);
+    if (need > ctx->pf_bytes) {
+        HY3A_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v);
+        ctx->d_pf_k = ctx->d_pf_v = NULL; ctx->pf_bytes = 0;
+        if (cudaMalloc(&ctx->d_pf_k, need) != cudaSuccess || cudaMalloc(&ctx->d_pf_v, need) != cudaSuccess) {
+            cudaFree(ctx->d_pf_k); ctx->d_pf_k = NULL;
+            return hy3a_fail(ctx, HY3A_ENOMEM, "prefill: cannot allocate 2 x %zu bytes of fp16 workspace", need);
+        }
+        ctx->pf_bytes = need;
+    }
+    hy3a_cache_view cv = hy3a_view(ctx);
+    dim3 g1(pages, kvh);
+    switch (ctx->cfg.kv_dtype) {
+        case 0: hy3a_kv_to_f16_kernel<0><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
+        case 1: hy3a_kv_to_f16_kernel<1><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
+        default: hy3a_kv_to_f16_kernel<2><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
+    }
+    ctx->launches++;
+    HY3A_CUDA(ctx, cudaGetLastError());
+
+    { const char *e = getenv("HY3A_PF_STOP"); if (e && atoi(e) == 1) return HY3A_OK; }   /* development: pass 1 only */
+    CUtensorMap tq, tk, tv;
+    {
+        const cuuint64_t dq[3] = {HY3A_D, HY3A_N_HEAD, (cuuint64_t)nq}, sq[2] = {HY3A_D * 2, HY3A_N_HEAD * HY3A_D * 2};
+        const cuuint32_t bq[3] = {64, 8, kQTok};
+        int rc = make_map(ctx, &tq, const_cast<void *>(q16), dq, sq, bq);
+        if (rc) return rc;
+        const cuuint64_t dk[3] = {HY3A_D, (cuuint64_t)tok_stride, (cuuint64_t)kvh}, sk[2] = {HY3A_D * 2, (cuuint64_t)tok_stride * HY3A_D * 2};
+        const cuuint32_t bk[3] = {64, kKeys, 1};
+        rc = make_map(ctx, &tk, ctx->d_pf_k, dk, sk, bk);
+        if (rc) return rc;
+        const cuuint64_t dv[3] = {(cuuint64_t)tok_stride, HY3A_D, (cuuint64_t)kvh}, sv[2] = {(cuuint64_t)tok_stride * 2, (cuuint64_t)tok_stride * HY3A_D * 2};
+        const cuuint32_t bv[3] = {64, HY3A_D, 1};
+        rc = make_map(ctx, &tv, ctx->d_pf_v, dv, sv, bv);
+        if (rc) return rc;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+        attr_set = true;
+    }
+    prefill_args a;
+    a.out = out; a.out_stride = out_stride; a.base = base_slot; a.nq = nq; a.kv_head_begin = ctx->cfg.kv_head_begin; a.err = ctx->d_err;
+    dim3 g2((nq + kQTok - 1) / kQTok, kvh);
+    hy3a_prefill_kernel<<<g2, kPfThreads, kPfSmem, ctx->stream>>>(tq, tk, tv, a);
+    ctx->launches++;
+    ctx->bulk_write_pending = 1;
+    HY3A_CUDA(ctx, cudaGetLastError());
+    return HY3A_OK;
 }
