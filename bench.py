@@ -55,7 +55,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -157,6 +157,51 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------- GPU arm
+def prefill_section(torch, dev, kv="fp16", prompt=8192, chunk=512):
+    """Secondary metric: chunked causal prefill attention, an 8192-token prompt in 512-token chunks,
+    FP16 KV cache, 64 Q / 8 KV heads, one layer (configs[2]).  TFLOP/s = 4*128*64*sum(pos+1) / device time
+    of the attention calls (fp16 gather pass + tcgen05 kernel); the fused append is timed separately."""
+    from hy3_b200 import Hy3Attn
+    ctx = Hy3Attn(kv_dtype=kv, n_layers=1, max_batch=chunk, max_tokens=prompt + 256, device=dev.index)
+    q = torch.randn((prompt, H, D), device=dev)
+    k = torch.randn((prompt, G, D), device=dev)
+    v = torch.randn((prompt, G, D), device=dev)
+    q16 = torch.empty((chunk, H, D), dtype=torch.float16, device=dev)
+    out = torch.zeros((chunk, H, D), device=dev)
+
+    def run():
+        att, app = [], []
+        for c in range(prompt // chunk):
+            b = c * chunk
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ctx.batch_set([0] * chunk, list(range(b, b + chunk)))
+            ev[0].record()
+            ctx.append(0, q[b:b + chunk], k[b:b + chunk], v[b:b + chunk], q_out16=q16)
+            ev[1].record()
+            ctx.prefill(0, 0, b, q16, out=out)
+            ev[2].record()
+            att.append((ev[1], ev[2])); app.append((ev[0], ev[1]))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in att), sum(a.elapsed_time(b) for a, b in app)
+    for _ in range(3):
+        run()
+    att_ms, app_ms = min(run() for _ in range(3))
+    ctx.sync()
+    launches = ctx.launches
+    ctx.close()
+    pairs = sum(c * chunk + i + 1 for c in range(prompt // chunk) for i in range(chunk))
+    flops = 4.0 * D * H * pairs
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = json.load(open(p))["bf16_tflops"] if os.path.exists(p) else 1590.0
+    tf = flops / att_ms / 1e9
+    return {"metric": "prefill_attn_TFLOPs", "value": tf, "unit": "TFLOP/s", "workload": "configs[2]: %d-token prompt in %d-token chunks, %s KV, 1 layer" % (prompt, chunk, kv),
+            "attention_ms_per_layer": att_ms, "append_ms_per_layer": app_ms, "algorithmic_tflop_per_layer": flops / 1e12,
+            "roofline": {"bound": "tensor", "kernel": "hy3a_prefill_kernel", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                         "frac_of_nominal_2250": tf / 2250.0,
+                         "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops, burst)" if os.path.exists(p) else "fallback 1.59 PFLOP/s"},
+            "gpu_launches_total": launches}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -239,15 +284,15 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- (1) device-resident throughput: W warm-up + K timed graph replays
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()          # samples clocks / throttle reasons from here to the end of the measurements
     step_no = 2
     for _ in range(args.warmup):
         set_positions(step_no); step_no += 1
         with torch.cuda.stream(stream):
             graph.replay()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     first_step = step_no
     e0.record(stream)
@@ -258,7 +303,6 @@ def run_ours(args):
     e1.record(stream)
     barrier()
     ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
     ctx.sync()
     if world > 1:
         t = torch.tensor([ms_total], device=dev)
@@ -310,9 +354,11 @@ def run_ours(args):
     tr = os.path.join(ROOT, "profiles", "decode_%s_traffic.json" % args.kv)
     if os.path.exists(tr):
         t = json.load(open(tr))
-        roofline["traffic"] = t["dram_bytes_per_token_kvhead_layer"] * (ntok0 + step_no + 1) * G
+        roofline["traffic"] = t["dram_bytes_per_token_layer"] * (ntok0 + step_no + 1)
         roofline["traffic_source"] = t["source"]
     ctx.sync()
+    prefill = prefill_section(torch, dev) if (rank == 0 and world == 1 and not args.no_prefill) else None
+    clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
         cpu = None
@@ -332,7 +378,7 @@ def run_ours(args):
                 "frac_of_hbm_peak": value / world / peak, "roofline": roofline, "cpu_baseline": cpu,
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_in.numel() * 4,
                         "d2h_bytes_per_step": host_out.numel() * 4},
-                "gpu_launches": per_step_launches * args.steps, "clocks": clocks}
+                "gpu_launches": per_step_launches * args.steps, "clocks": clocks, "prefill": prefill}
         print(json.dumps(line))
     ctx.close()
     if world > 1:
@@ -342,7 +388,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kv", default="int8", choices=["int8", "int4", "fp16"])
@@ -350,11 +396,19 @@ def main():
     ap.add_argument("--ntok", type=int, default=NTOK)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the secondary chunked-prefill measurement")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the chunked-prefill measurement and print its JSON object")
+    ap.add_argument("--prefill-prompt", type=int, default=8192)
+    ap.add_argument("--prefill-kv", default="fp16", choices=["int8", "int4", "fp16"])
     ap.add_argument("--two-kernels", action="store_true", help="append and decode as separate launches instead of the fused step")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.prefill_only:
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps(prefill_section(torch, torch.device("cuda", 0), kv=args.prefill_kv, prompt=args.prefill_prompt)))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
