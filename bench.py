@@ -239,11 +239,14 @@ def run_ours(args):
         qo = torch.empty((n_layers, 1, H, D), dtype=torch.float32, device=dev)
         out = torch.zeros((n_layers, 1, H, D), dtype=torch.float32, device=dev)
     owner = (rank == world - 1)                      # sequence sharding: the tail rank appends the new token
-    sharded = make_cuda_sharded_decode(ctx, 1) if world > 1 else None
+    sharded = make_cuda_sharded_decode(ctx, 1, n_slots=2) if world > 1 else None
+    side = torch.cuda.Stream(device=dev) if world > 1 else None   # the per-layer exchange runs here, under the next layer's stream of KV
 
     def layer_views(l):
         row = x[l]
         return (row[:H * D].view(1, H, D), row[H * D:H * D + G * D].view(1, G, D), row[H * D + G * D:].view(1, G, D))
+
+    slot_free = [None, None]
 
     def enqueue_step():
         """All launches of one step on `stream` (captured into a graph once)."""
@@ -257,8 +260,27 @@ def run_ours(args):
                     sharded.step(l, qo[l], out[l])
             elif sharded is None:
                 ctx.decode_step(l, q, k, v, out=out[l])        # fused norm+RoPE+quantise/append + attention
-            else:
+            elif args.serial_exchange:
                 sharded.step(l, (q, k if owner else None, v if owner else None), out[l])
+            else:
+                # layers are independent: layer l's all-gather + merge overlap layer l+1's KV stream
+                slot = l & 1
+                if l >= 2:
+                    stream.wait_event(slot_free[slot])          # buffers of layer l-2 have been merged
+                sharded.partial(l, (q, k if owner else None, v if owner else None), slot)
+                ready = torch.cuda.Event()
+                ready.record(stream)
+                side.wait_event(ready)
+                ctx.set_stream(side)
+                with torch.cuda.stream(side):
+                    sharded.exchange_merge(slot, out[l])
+                    slot_free[slot] = torch.cuda.Event()
+                    slot_free[slot].record(side)
+                ctx.set_stream(stream)
+        if sharded is not None and not args.serial_exchange and not args.two_kernels:
+            for e in slot_free:
+                if e is not None:
+                    stream.wait_event(e)                         # join the side stream
 
     def set_positions(step):
         local_slot = ntok0 + step if owner else ntok0 - 1
@@ -336,12 +358,18 @@ def run_ours(args):
     set_positions(step_no)
     reps = max(1, 240 // n_layers)
     with torch.cuda.stream(stream):
+        def one(l):
+            q, k, v = layer_views(l)
+            if args.two_kernels:
+                ctx.decode(l, qo[l], out=out[l])
+            else:
+                ctx.decode_step(l, q, k if owner else None, v if owner else None, out=out[l])   # the kernel a step launches
         for l in range(min(n_layers, 8)):
-            ctx.decode(l, qo[l], out=out[l])
+            one(l)
         e0.record(stream)
         for _ in range(reps):
             for l in range(n_layers):
-                ctx.decode(l, qo[l], out=out[l])
+                one(l)
         e1.record(stream)
     stream.synchronize()
     k_ms = e0.elapsed_time(e1) / (reps * n_layers)
@@ -371,7 +399,7 @@ def run_ours(args):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD if (world == 1 and args.kv == "int8" and n_layers == N_LAYERS and ntok0 == NTOK)
                            else "%s-KV decode, %d layers x %d positions per GPU, %d GPU(s)%s" % (
-                               args.kv, n_layers, ntok0, world, ", sequence-sharded with NCCL all-gather LSE merge" if world > 1 else ""),
+                               args.kv, n_layers, ntok0, world, (", sequence-sharded with NCCL all-gather LSE merge" + (" (exchange of layer l under the KV stream of layer l+1)" if not args.serial_exchange else " (dependent chain)")) if world > 1 else ""),
                            "kv_dtype": args.kv, "layers": n_layers, "positions_per_gpu": ntok0, "compute": "fp16 mma.sync, fp32 accumulate/softmax",
                            "l2": "inputs larger than L2: %.2f GB of KV streamed per step, every layer's cache read once" % (bytes_per_step / world / 1e9),
                            "graph": "one CUDA graph of %d launches per step" % per_step_launches},
@@ -379,13 +407,22 @@ def run_ours(args):
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_in.numel() * 4,
                         "d2h_bytes_per_step": host_out.numel() * 4},
                 "gpu_launches": per_step_launches * args.steps, "clocks": clocks, "prefill": prefill}
-        print(json.dumps(line))
-    ctx.close()
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # tearing the NCCL communicator down while a captured graph still references it can stall;
+        # everything is measured and printed, so leave without the teardown
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+    del graph
+    ctx.close()
 
 
 def main():
+    if os.environ.get("HY3_BENCH_WATCHDOG"):     # development aid: dump the Python stacks if the run stalls
+        import faulthandler
+        faulthandler.dump_traceback_later(int(os.environ["HY3_BENCH_WATCHDOG"]), exit=True)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -400,6 +437,7 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="run only the chunked-prefill measurement and print its JSON object")
     ap.add_argument("--prefill-prompt", type=int, default=8192)
     ap.add_argument("--prefill-kv", default="fp16", choices=["int8", "int4", "fp16"])
+    ap.add_argument("--serial-exchange", action="store_true", help="N>1: all-gather + merge of a layer before the next layer starts (dependent chain)")
     ap.add_argument("--two-kernels", action="store_true", help="append and decode as separate launches instead of the fused step")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -37,28 +37,39 @@ def sequence_range(rank, world, ntok, align=128):
 
 
 class SequenceShardedDecode:
-    """Per-layer decode step of a sequence-sharded cache: local partials -> all-gather -> merge."""
+    """Per-layer decode step of a sequence-sharded cache: local partials -> all-gather -> merge.
 
-    def __init__(self, partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty_like):
+    The two halves are separate methods so that a caller whose layers are independent (or that has
+    other work between attention and its consumer) can run the exchange of layer l on a side
+    stream while layer l+1 streams its KV: `partial(layer, q, slot)` then, later,
+    `exchange_merge(slot, out)`; `n_slots` buffer sets let that many exchanges be in flight."""
+
+    def __init__(self, partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty_like, n_slots=1):
         """partial_fn(layer, q, partial_buf): fill [n_rows, n_heads, 130] for the local token range;
         merge_fn(gathered, n_parts, out): fold [world, n_rows, n_heads, 130] in rank order;
         all_gather_fn(gathered, local): the collective; empty_like(shape): buffer factory."""
         self.partial_fn, self.merge_fn, self.all_gather_fn = partial_fn, merge_fn, all_gather_fn
         self.world, self.n_rows, self.n_heads = world, n_rows, n_heads
-        self.local = empty_like((n_rows, n_heads, PARTIAL_FLOATS))
-        self.gathered = empty_like((world, n_rows, n_heads, PARTIAL_FLOATS))
+        self.local = [empty_like((n_rows, n_heads, PARTIAL_FLOATS)) for _ in range(n_slots)]
+        self.gathered = [empty_like((world, n_rows, n_heads, PARTIAL_FLOATS)) for _ in range(n_slots)]
 
-    def step(self, layer, q, out):
-        self.partial_fn(layer, q, self.local)
+    def partial(self, layer, q, slot=0):
+        self.partial_fn(layer, q, self.local[slot])
+
+    def exchange_merge(self, slot, out):
         if self.world == 1:
-            self.merge_fn(self.local, 1, out)
+            self.merge_fn(self.local[slot], 1, out)
         else:
-            self.all_gather_fn(self.gathered, self.local)
-            self.merge_fn(self.gathered, self.world, out)
+            self.all_gather_fn(self.gathered[slot], self.local[slot])
+            self.merge_fn(self.gathered[slot], self.world, out)
         return out
 
+    def step(self, layer, q, out):
+        self.partial(layer, q, 0)
+        return self.exchange_merge(0, out)
 
-def make_cuda_sharded_decode(ctx, n_rows, group=None):
+
+def make_cuda_sharded_decode(ctx, n_rows, group=None, n_slots=1):
     """Wire SequenceShardedDecode to a Hy3Attn context and torch.distributed (NCCL)."""
     import torch
     import torch.distributed as dist
@@ -81,7 +92,7 @@ def make_cuda_sharded_decode(ctx, n_rows, group=None):
     def empty(shape):
         return torch.empty(shape, dtype=torch.float32, device=dev)
 
-    return SequenceShardedDecode(partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty)
+    return SequenceShardedDecode(partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty, n_slots)
 
 
 def merge_partials_numpy(gathered):
