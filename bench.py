@@ -240,6 +240,13 @@ def run_ours(args):
         out = torch.zeros((n_layers, 1, H, D), dtype=torch.float32, device=dev)
     owner = (rank == world - 1)                      # sequence sharding: the tail rank appends the new token
     sharded = make_cuda_sharded_decode(ctx, 1, n_slots=2) if world > 1 else None
+    if world > 1 and not args.nccl_exchange:
+        # exchange fused into the kernels: every rank's decode epilogue stores its records into all ranks'
+        # gather buffers over NVLink; handles travel once through torch.distributed
+        handles = [None] * world
+        dist.all_gather_object(handles, ctx.shard_init(rank, world, n_layers, 1))
+        ctx.shard_connect(handles)
+        dist.barrier()
     side = torch.cuda.Stream(device=dev) if world > 1 else None   # the per-layer exchange runs here, under the next layer's stream of KV
 
     def layer_views(l):
@@ -260,6 +267,9 @@ def run_ours(args):
                     sharded.step(l, qo[l], out[l])
             elif sharded is None:
                 ctx.decode_step(l, q, k, v, out=out[l])        # fused norm+RoPE+quantise/append + attention
+            elif not args.nccl_exchange:
+                # the exchange is inside the kernel: one launch per layer produces the merged output on every rank
+                ctx.decode_step_sharded(l, l, q, k if owner else None, v if owner else None, out=out[l])
             elif args.serial_exchange:
                 sharded.step(l, (q, k if owner else None, v if owner else None), out[l])
             else:
@@ -399,7 +409,7 @@ def run_ours(args):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD if (world == 1 and args.kv == "int8" and n_layers == N_LAYERS and ntok0 == NTOK)
                            else "%s-KV decode, %d layers x %d positions per GPU, %d GPU(s)%s" % (
-                               args.kv, n_layers, ntok0, world, (", sequence-sharded with NCCL all-gather LSE merge" + (" (exchange of layer l under the KV stream of layer l+1)" if not args.serial_exchange else " (dependent chain)")) if world > 1 else ""),
+                               args.kv, n_layers, ntok0, world, (", sequence-sharded, " + ("NCCL all-gather" if args.nccl_exchange else "records pushed over NVLink peer memory by the decode kernel") + " + LSE merge" + (" (exchange of layer l under the KV stream of layer l+1)" if not args.serial_exchange else " (dependent chain)")) if world > 1 else ""),
                            "kv_dtype": args.kv, "layers": n_layers, "positions_per_gpu": ntok0, "compute": "fp16 mma.sync, fp32 accumulate/softmax",
                            "l2": "inputs larger than L2: %.2f GB of KV streamed per step, every layer's cache read once" % (bytes_per_step / world / 1e9),
                            "graph": "one CUDA graph of %d launches per step" % per_step_launches},
@@ -437,6 +447,7 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="run only the chunked-prefill measurement and print its JSON object")
     ap.add_argument("--prefill-prompt", type=int, default=8192)
     ap.add_argument("--prefill-kv", default="fp16", choices=["int8", "int4", "fp16"])
+    ap.add_argument("--nccl-exchange", action="store_true", help="N>1: exchange the partial records with an NCCL all-gather instead of peer-memory stores from the kernel")
     ap.add_argument("--serial-exchange", action="store_true", help="N>1: all-gather + merge of a layer before the next layer starts (dependent chain)")
     ap.add_argument("--two-kernels", action="store_true", help="append and decode as separate launches instead of the fused step")
     args = ap.parse_args()

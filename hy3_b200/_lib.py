@@ -45,6 +45,11 @@ PROTOTYPES = {
     "hy3a_decode": (_i, [_vp, _i, _vp, _sz, _vp, _sz, _vp]),
     "hy3a_decode_step": (_i, [_vp, _i, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp]),
     "hy3a_decode_noalloc": (_i, [_vp, _i, _vp, _sz, _vp, _sz]),
+    "hy3a_shard_init": (_i, [_vp, _i, _i, _i, _i, _vp]),
+    "hy3a_shard_connect": (_i, [_vp, _vp]),
+    "hy3a_shard_disconnect": (_i, [_vp]),
+    "hy3a_shard_connect_local": (_i, [_vp]),
+    "hy3a_decode_step_sharded": (_i, [_vp, _i, _i, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz]),
     "hy3a_merge_partials": (_i, [_vp, _vp, _i, _i, _i, _vp, _sz]),
     "hy3a_prefill": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _sz]),
     "hy3a_export_kv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp]),

@@ -165,6 +165,34 @@ class Hy3Attn:
                                             0 if out is None else out.stride(0), _ptr(partials)))
         return out if partials is None else partials
 
+    # ---- sequence sharding over peer memory
+    def shard_init(self, rank, world, n_slots, n_rows):
+        """Allocate this rank's gather buffer; returns its 64-byte IPC handle (bytes)."""
+        buf = C.create_string_buffer(64)
+        self._chk(self.lib.hy3a_shard_init(self.h, rank, world, n_slots, n_rows, buf))
+        return bytes(buf.raw)
+
+    def shard_connect(self, handles):
+        """handles: the IPC handles of all ranks, in rank order."""
+        blob = b"".join(handles)
+        self._chk(self.lib.hy3a_shard_connect(self.h, C.c_char_p(blob)))
+
+    def shard_disconnect(self):
+        self._chk(self.lib.hy3a_shard_disconnect(self.h))
+
+    def shard_connect_local(self):
+        """Silent stand-ins for the other ranks (single-process bring-up and tests)."""
+        self._chk(self.lib.hy3a_shard_connect_local(self.h))
+
+    def decode_step_sharded(self, layer, slot, q, k, v, out=None):
+        """hy3a_decode_step over this rank's tokens + in-kernel exchange and fold: `out` is the attention over ALL ranks' tokens."""
+        if out is None:
+            import torch
+            out = torch.empty((self.batch_n, 64, 128), dtype=torch.float32, device=q.device)
+        self._chk(self.lib.hy3a_decode_step_sharded(self.h, layer, slot, _ptr(q), q.stride(0), _ptr(k), 0 if k is None else k.stride(0),
+                                                    _ptr(v), 0 if v is None else v.stride(0), _ptr(out), out.stride(0)))
+        return out
+
     def merge_partials(self, partials, n_parts, n_rows, n_heads, out):
         assert partials.is_contiguous() and partials.numel() == n_parts * n_rows * n_heads * PARTIAL_FLOATS
         self._chk(self.lib.hy3a_merge_partials(self.h, _ptr(partials), n_parts, n_rows, n_heads, _ptr(out), out.stride(0)))

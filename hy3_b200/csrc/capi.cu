@@ -109,6 +109,8 @@ void hy3a_destroy(hy3a_ctx *ctx) {
     cudaFree(ctx->pool); cudaFree(ctx->d_block_table); cudaFree(ctx->d_vs_max); cudaFree(ctx->d_inv_freq);
     cudaFree(ctx->d_norm_w); cudaFree(ctx->d_batch); cudaFree(ctx->d_partials); cudaFree(ctx->d_counters); cudaFree(ctx->d_err);
     cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v); cudaFree(ctx->d_trace);
+    hy3a_shard_disconnect(ctx);
+    cudaFree(ctx->shard_local);
     if (ctx->h_ring) cudaFreeHost(ctx->h_ring);
     if (ctx->h_err) cudaFreeHost(ctx->h_err);
     for (int i = 0; i < HY3A_RING_SLOTS; i++) if (ctx->ring_ev[i]) cudaEventDestroy(ctx->ring_ev[i]);
@@ -150,6 +152,7 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     hy3a_ctx *ctx = (hy3a_ctx *)calloc(1, sizeof(hy3a_ctx));
     if (!ctx) return hy3a_fail(NULL, HY3A_ENOMEM, "calloc failed");
     ctx->cfg = *cfg;
+    ctx->shard_slot = -1;
     ctx->cfg.device = dev;
     ctx->device = dev;
     ctx->geom = hy3a_make_geom(cfg->kv_dtype);
@@ -400,6 +403,89 @@ int hy3a_decode_step(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_strid
     st.q_in = q_in; st.k_in = k_in; st.v_in = v_in; st.q_stride = q_stride; st.k_stride = k_stride; st.v_stride = v_stride;
     st.q_out = q_out; st.q_out_stride = q_out_stride;
     return hy3a_launch_decode(ctx, layer, NULL, 0, out, out_stride, partials, &st);
+}
+
+/* ---- sequence-shard exchange over peer memory ------------------------------------------------ */
+int hy3a_shard_init(hy3a_ctx *ctx, int rank, int world, int n_slots, int n_rows, unsigned char *handle_out) {
+    if (!ctx) return HY3A_EINVAL;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || n_slots < 1 || n_rows < 1 || n_rows > ctx->cfg.max_batch || !handle_out)
+        return hy3a_fail(ctx, HY3A_EINVAL, "shard_init: bad argument (rank %d of %d, %d slots, %d rows)", rank, world, n_slots, n_rows);
+    if (ctx->shard_local) return hy3a_fail(ctx, HY3A_ESTATE, "shard_init: already initialised");
+    const size_t n_seg = (size_t)n_rows * ctx->cfg.kv_head_count;
+    const size_t slice = n_seg * 8 * (HY3A_PARTIAL_FLOATS / 2) * 16;    /* flagged 16-byte lines: 2 values each */
+    ctx->shard_state_off = ((size_t)n_slots * world * slice + 255) & ~(size_t)255;
+    ctx->shard_bytes = ctx->shard_state_off + (size_t)n_slots * n_seg * sizeof(unsigned);   /* use count per (slot, segment) */
+    HY3A_CUDA(ctx, cudaMalloc(&ctx->shard_local, ctx->shard_bytes));
+    HY3A_CUDA(ctx, cudaMemset(ctx->shard_local, 0, ctx->shard_bytes));
+    cudaIpcMemHandle_t h;
+    HY3A_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->shard_local));
+    memcpy(handle_out, &h, sizeof(h));
+    ctx->shard_rank = rank; ctx->shard_world = world; ctx->shard_slots = n_slots; ctx->shard_rows = n_rows;
+    for (int r = 0; r < 8; r++) ctx->shard_peer[r] = NULL;
+    ctx->shard_peer[rank] = ctx->shard_local;
+    return HY3A_OK;
+}
+
+int hy3a_shard_connect(hy3a_ctx *ctx, const unsigned char *handles) {
+    if (!ctx || !handles) return HY3A_EINVAL;
+    if (!ctx->shard_local) return hy3a_fail(ctx, HY3A_ESTATE, "shard_connect: call hy3a_shard_init first");
+    for (int r = 0; r < ctx->shard_world; r++) {
+        if (r == ctx->shard_rank || ctx->shard_peer[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * sizeof(h), sizeof(h));
+        void *p = NULL;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return hy3a_fail(ctx, HY3A_ECUDA, "shard_connect: cudaIpcOpenMemHandle(rank %d): %s", r, cudaGetErrorString(e));
+        ctx->shard_peer[r] = (unsigned char *)p;
+    }
+    return HY3A_OK;
+}
+
+int hy3a_shard_connect_local(hy3a_ctx *ctx) {
+    if (!ctx) return HY3A_EINVAL;
+    if (!ctx->shard_local) return hy3a_fail(ctx, HY3A_ESTATE, "shard_connect_local: call hy3a_shard_init first");
+    for (int r = 0; r < ctx->shard_world; r++) {
+        if (r == ctx->shard_rank || ctx->shard_peer[r]) continue;
+        void *p = NULL;
+        HY3A_CUDA(ctx, cudaMalloc(&p, ctx->shard_bytes));
+        HY3A_CUDA(ctx, cudaMemset(p, 0, ctx->shard_bytes));
+        ctx->shard_peer[r] = (unsigned char *)p;
+        ctx->shard_standin |= 1 << r;
+    }
+    return HY3A_OK;
+}
+
+int hy3a_shard_disconnect(hy3a_ctx *ctx) {
+    if (!ctx) return HY3A_EINVAL;
+    for (int r = 0; r < ctx->shard_world; r++) {
+        if (r == ctx->shard_rank || !ctx->shard_peer[r]) continue;
+        if (ctx->shard_standin & (1 << r)) cudaFree(ctx->shard_peer[r]);
+        else cudaIpcCloseMemHandle(ctx->shard_peer[r]);
+        ctx->shard_peer[r] = NULL;
+    }
+    ctx->shard_standin = 0;
+    return HY3A_OK;
+}
+
+int hy3a_decode_step_sharded(hy3a_ctx *ctx, int layer, int slot, const float *q_in, size_t q_stride, const float *k_in, size_t k_stride,
+                             const float *v_in, size_t v_stride, float *out, size_t out_stride) {
+    int rc = check_layer(ctx, layer, "decode_step_sharded");
+    if (rc) return rc;
+    if (!ctx->shard_local) return hy3a_fail(ctx, HY3A_ESTATE, "decode_step_sharded: call hy3a_shard_init / hy3a_shard_connect first");
+    for (int r = 0; r < ctx->shard_world; r++) if (!ctx->shard_peer[r]) return hy3a_fail(ctx, HY3A_ESTATE, "decode_step_sharded: rank %d not connected", r);
+    if (slot < 0 || slot >= ctx->shard_slots) return hy3a_fail(ctx, HY3A_EINVAL, "decode_step_sharded: slot %d out of range", slot);
+    if (ctx->batch_n != ctx->shard_rows) return hy3a_fail(ctx, HY3A_EINVAL, "decode_step_sharded: batch has %d rows, the exchange was set up for %d", ctx->batch_n, ctx->shard_rows);
+    if (!q_in || !out || (!k_in) != (!v_in)) return hy3a_fail(ctx, HY3A_EINVAL, "decode_step_sharded: NULL argument");
+    if (((uintptr_t)q_in | (uintptr_t)k_in | (uintptr_t)v_in | (uintptr_t)out) & 15 || ((q_stride | k_stride | v_stride | out_stride) & 3))
+        return hy3a_fail(ctx, HY3A_EINVAL, "decode_step_sharded: pointers must be 16-byte aligned, strides multiples of 4");
+    if (ctx->decode_stages < 2) return hy3a_fail(ctx, HY3A_ESTATE, "decode_step_sharded: needs the page ring (HY3A_DECODE_STAGES >= 2)");
+    hy3a_step_inputs st;
+    st.q_in = q_in; st.k_in = k_in; st.v_in = v_in; st.q_stride = q_stride; st.k_stride = k_stride; st.v_stride = v_stride;
+    st.q_out = NULL; st.q_out_stride = 0;
+    ctx->shard_slot = slot;
+    rc = hy3a_launch_decode(ctx, layer, NULL, 0, out, out_stride, NULL, &st);
+    ctx->shard_slot = -1;
+    return rc;
 }
 
 int hy3a_merge_partials(hy3a_ctx *ctx, const float *partials, int n_parts, int n_rows, int n_heads, float *out, size_t out_stride) {

@@ -86,6 +86,16 @@ struct hy3a_ctx {
     int use_pdl;          /* launch kernels with programmatic stream serialization (HY3A_NO_PDL=1 turns it off) */
     int decode_stages;    /* pages in the decode kernel's shared-memory ring; < 2 selects the direct-load variant */
 
+    /* sequence-shard exchange over peer memory (hy3a_shard_*): one allocation per rank =
+     * [n_slots][world][rows*heads][65] flagged 16-byte lines {value, flag, value, flag} of gathered records,
+     * then one use count per (slot, row, KV head) */
+    unsigned char *shard_local;
+    unsigned char *shard_peer[8];     /* every rank's allocation as mapped into this process ([rank] = shard_local) */
+    size_t shard_state_off, shard_bytes;
+    int shard_rank, shard_world, shard_slots, shard_rows;
+    int shard_standin;                /* bit r: shard_peer[r] is a stand-in allocated by this process */
+    int shard_slot;                   /* >= 0 while hy3a_decode_step_sharded is launching */
+
     hy3a_rope_params rope;
     uint64_t launches;
     char err[512];

@@ -158,6 +158,15 @@ struct decode_args {
     float *out;
     size_t out_stride;
     float *user_partials; /* NULL or [n][8*kv_heads][130] */
+    /* sequence sharding with the exchange inside the kernel (n_dest = world size > 0): the CTA that completes a
+     * (row, KV head) segment stores its 8 records, as 16-byte lines {value, flag, value, flag}, into every other
+     * rank's gather buffer (dest[r], already offset to this rank's slice there), then polls the lines the other
+     * ranks store into its own buffer, folds all ranks' records in rank order and writes the final output.
+     * flag = use count of the (slot, segment) + 1, kept in shard_round on every rank.                          */
+    int n_dest, my_rank;
+    uint4 *dest[8];
+    const uint4 *gathered;        /* local: [n_dest][n*kv_heads*8][65] lines of the slot */
+    unsigned *shard_round;        /* local: [n*kv_heads] uses of the slot so far */
     float *scratch;       /* [(gridDim.x + n*kv_heads)][8][130] */
     unsigned int *counters;
     unsigned int *err;
@@ -422,7 +431,122 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, float qf, c
 /* DIRECT variant (STAGED=false): operands fetched straight from global memory with 128-bit
  * loads (no ring, no producer).  STAGED variant: kWarps consumer warps + 1 producer warp.
  * Same arithmetic, same results.                                                          */
-template <int DT, bool STAGED>
+/* Sequence sharding: lines of one head's record in a gather buffer: line 0 = {m, l}, line 1 + j = acc[2j], acc[2j+1]. */
+constexpr int kShardLines = HY3A_PARTIAL_FLOATS / 2;   /* 65 */
+__device__ __forceinline__ void shard_store_line(uint4 *p, float x, float y, unsigned flag) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(p), "r"(__float_as_uint(x)), "r"(flag), "r"(__float_as_uint(y)) : "memory");
+}
+__device__ __forceinline__ uint4 shard_load_line(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+/* Sequence sharding, receiving side; run by the first 8 warps of one CTA for one (row, KV head) segment: thread
+ * (h, d4) polls the three lines it needs of every other rank's record (all ranks' loads are issued before any is
+ * checked, so the usual cost is one L2 round trip), takes its own rank's values from registers, folds in rank
+ * order with the rule of hy3_gpu.cu:233-247 (same order on every rank: identical bits) and writes the normalised
+ * output.  The wait is bounded in polls and in time (about a second); when it runs out a code goes into the
+ * error word, later waits return at once and the kernel runs to its end.                                      */
+struct shard_fold_args {
+    const uint4 *rec0;     /* line 0 of rank 0's record of this thread's (segment, head) */
+    size_t rank_stride;    /* lines between consecutive ranks' records */
+    unsigned *err;
+    float *out;            /* this thread's 4 output floats */
+    const uint4 *stage;    /* shared memory, [kShardBatch][8 heads][65] lines: landing zone of the polls */
+    int n_ranks, my_rank, line_a, h, lane;
+    unsigned flag;
+    float own_m, own_l, own_acc[4];
+};
+constexpr int kShardBatch = 5;   /* ranks polled at once: 5 x 8 320 bytes fit the per-warp output staging area */
+static_assert(kShardBatch * 8 * kShardLines * 16 <= kFixedO, "landing zone of the rank records exceeds the staging area");
+
+/* Run by the first 8 warps (all lanes) for one segment.  Polling costs no registers: every thread copies the three
+ * lines it needs of each pending rank's record into shared memory with 16-byte asynchronous copies (L2 -> shared),
+ * all ranks of a batch in flight at once, and checks the flags there; the usual cost is one L2 round trip per batch.
+ * Own rank: values from registers.  Fold in rank order (hy3_gpu.cu:233-247): identical bits on every rank.
+ * The wait is bounded in polls and in time (about a second); when it runs out a code goes into the error word, the
+ * missing records count as empty, later waits return at once and the kernel runs to its end.                       */
+__device__ __forceinline__ void shard_fold(const shard_fold_args &a) {
+    float ms = -INFINITY, ss = 0.f, ov[4] = {0.f, 0.f, 0.f, 0.f};
+    const unsigned stage_u32 = smem_u32(a.stage);
+#pragma unroll 1
+    for (int base = 0; base < a.n_ranks; base += kShardBatch) {
+        const int cnt = min(kShardBatch, a.n_ranks - base);
+        unsigned pending = 0u;   /* bit j: rank base + j not complete yet (per thread) */
+        for (int j = 0; j < cnt; j++) if (base + j != a.my_rank) pending |= 1u << j;
+        unsigned long long t0 = 0;
+        bool gave_up = false;
+#pragma unroll 1
+        for (unsigned i = 0; __any_sync(0xffffffffu, pending != 0u); i++) {
+#pragma unroll 1
+            for (int j = 0; j < cnt; j++)
+                if (pending & (1u << j)) {
+                    const uint4 *rec = a.rec0 + (size_t)(base + j) * a.rank_stride;
+                    const unsigned dst = stage_u32 + (unsigned)((j * 8 + a.h) * kShardLines) * 16u;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * (unsigned)a.line_a), "l"(rec + a.line_a) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * (unsigned)(a.line_a + 1)), "l"(rec + a.line_a + 1) : "memory");
+                    if (a.lane == 0) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(rec) : "memory");
+                }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncwarp();
+#pragma unroll 1
+            for (int j = 0; j < cnt; j++)
+                if (pending & (1u << j)) {
+                    const uint4 *st = a.stage + (j * 8 + a.h) * kShardLines;
+                    const uint4 l0 = st[0];
+                    if (l0.y != a.flag || l0.w != a.flag) continue;
+                    if (__uint_as_float(l0.z) > 0.f) {
+                        const uint4 la = st[a.line_a], lb = st[a.line_a + 1];
+                        if (la.y != a.flag || la.w != a.flag || lb.y != a.flag || lb.w != a.flag) continue;
+                    }
+                    pending &= ~(1u << j);
+                }
+            __syncwarp();   /* lane 0 may overwrite line 0 in the next round */
+            if ((i & 15u) == 15u) {
+                bool stop = *reinterpret_cast<volatile unsigned *>(a.err) != 0u;
+                if (!stop && pending) {
+                    unsigned long long t1;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                    if (t0 == 0) t0 = t1;
+                    if (t1 - t0 > 1000000000ull || i > (1u << 24)) {
+                        if (atomicCAS(a.err, 0u, 3u) == 0u) a.err[1] = 41u;
+                        stop = true;
+                    }
+                }
+                if (__any_sync(0xffffffffu, stop && pending)) { gave_up = true; break; }
+                __nanosleep(32);
+            }
+        }
+#pragma unroll 1
+        for (int j = 0; j < cnt; j++) {
+            float pm, pl, pv[4];
+            if (base + j == a.my_rank) {
+                pm = a.own_m; pl = a.own_l; pv[0] = a.own_acc[0]; pv[1] = a.own_acc[1]; pv[2] = a.own_acc[2]; pv[3] = a.own_acc[3];
+                if (!(pl > 0.f)) continue;
+            } else {
+                if (gave_up && (pending & (1u << j))) continue;
+                const uint4 *st = a.stage + (j * 8 + a.h) * kShardLines;
+                const uint4 l0 = st[0];
+                pm = __uint_as_float(l0.x); pl = __uint_as_float(l0.z);
+                if (!(pl > 0.f)) continue;
+                const uint4 la = st[a.line_a], lb = st[a.line_a + 1];
+                pv[0] = __uint_as_float(la.x); pv[1] = __uint_as_float(la.z); pv[2] = __uint_as_float(lb.x); pv[3] = __uint_as_float(lb.z);
+            }
+            const float nm = fmaxf(ms, pm), os = __expf(ms - nm), rs = __expf(pm - nm);
+            ss = ss * os + pl * rs;
+            ov[0] = ov[0] * os + pv[0] * rs; ov[1] = ov[1] * os + pv[1] * rs; ov[2] = ov[2] * os + pv[2] * rs; ov[3] = ov[3] * os + pv[3] * rs;
+            ms = nm;
+        }
+        __syncwarp();   /* the landing zone is reused by the next batch of ranks */
+    }
+    const float inv = ss > 0.f ? 1.f / ss : 0.f;
+    *reinterpret_cast<float4 *>(a.out) = make_float4(ov[0] * inv, ov[1] * inv, ov[2] * inv, ov[3] * inv);
+}
+
+/* SHARD: the sequence-sharded variant (exchange + final fold in the epilogue); a separate instantiation so that the
+ * single-GPU kernel's register allocation is untouched by it. */
+template <int DT, bool STAGED, bool SHARD = false>
 __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_kernel(hy3a_cache_view cache, hy3a_batch_view batch, decode_args a) {
     /* dynamic shared memory: [s_o | s_ml | s_q | page-count prefix | full[8] empty[8] | ring of pages] */
     extern __shared__ __align__(128) uint8_t s_dyn[];
@@ -545,6 +669,18 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     /* rows with no keys on this rank: zero output / empty partial (hy3_gpu.cu:197-199) */
     for (int i = cta; i < n; i += gridDim.x) {
         if (s_prefix[i + 1] != s_prefix[i]) continue;
+        if (SHARD) {
+            /* sharded: the empty record {m = -inf, l = 0} of every head goes to every other rank now (one flagged line;
+             * the fold skips it without reading acc); this rank's own fold of the row happens at the end of the kernel,
+             * when the other ranks' records are due */
+            if (is_producer) continue;
+            for (int e = tid; e < G * 8; e += kThreads) {
+                const unsigned flag = a.shard_round[i * G + (e >> 3)] + 1u;
+                for (int r = 0; r < a.n_dest; r++)
+                    if (r != a.my_rank) shard_store_line(a.dest[r] + ((size_t)i * G * 8 + e) * kShardLines, -INFINITY, 0.f, flag);
+            }
+            continue;
+        }
         for (int e = tid; e < G * 8 * HY3A_D && !is_producer; e += kThreads) {
             int hq = e / HY3A_D, d = e % HY3A_D;
             if (a.user_partials) {
@@ -557,7 +693,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
         }
     }
 
-    if (idle) return;
+    if (idle && !SHARD) return;   /* sharded: idle CTAs may still own the fold of rows without local keys */
 
     if (warp == 0) TRACE(1);
 
@@ -888,6 +1024,35 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             consumer_sync();   /* the landing zone is read; the next segment may reuse the buffer */
             if (warp == 0) TRACE(26);
         }
+        if (SHARD) {
+            /* sequence sharding: this rank's records of the segment go into every other rank's gather buffer as
+             * flagged lines (no fence, no separate flag: a line is valid when both of its flag words carry this
+             * use's number), then the same threads collect the other ranks' lines and finish the segment */
+            const int seg = row * G + hl;
+            if (red) {
+                const unsigned flag = a.shard_round[seg] + 1u;
+                const float m_nat = M * kLn2;
+                const size_t ro = ((size_t)seg * 8 + h) * kShardLines;
+                for (int r = 0; r < a.n_dest; r++) {
+                    if (r == a.my_rank) continue;
+                    uint4 *rec = a.dest[r] + ro;
+                    if (d4 == 0) shard_store_line(rec, m_nat, L, flag);
+                    shard_store_line(rec + 1 + (d4 >> 1), acc[0], acc[1], flag);
+                    shard_store_line(rec + 2 + (d4 >> 1), acc[2], acc[3], flag);
+                }
+                if (warp == 0) TRACE(27);
+                shard_fold_args fa;
+                fa.rec0 = a.gathered + ro; fa.rank_stride = (size_t)n * G * 8 * kShardLines; fa.err = a.err;
+                fa.out = a.out + (size_t)row * a.out_stride + ((size_t)(cache.kv_head_begin + hl) * 8 + h) * HY3A_D + d4;
+                fa.n_ranks = a.n_dest; fa.my_rank = a.my_rank; fa.line_a = 1 + (d4 >> 1); fa.flag = flag; fa.stage = reinterpret_cast<const uint4 *>(s_dyn); fa.h = h; fa.lane = lane;
+                fa.own_m = m_nat; fa.own_l = L; fa.own_acc[0] = acc[0]; fa.own_acc[1] = acc[1]; fa.own_acc[2] = acc[2]; fa.own_acc[3] = acc[3];
+                shard_fold(fa);
+                if (warp == 0) TRACE(30);
+            }
+            consumer_sync();                 /* every thread has read the use count */
+            if (tid == 0) a.shard_round[seg] += 1u;
+            continue;
+        }
         if (!red) continue;
         if (a.user_partials) {
             float *rec = a.user_partials + ((size_t)row * G * 8 + (size_t)hl * 8 + h) * HY3A_PARTIAL_FLOATS;
@@ -899,6 +1064,25 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             *reinterpret_cast<float4 *>(a.out + (size_t)row * a.out_stride + head_q * HY3A_D + d4) = o4;
         }
     }
+    /* sharded: rows without keys on this rank were announced at the top; the other ranks' records are folded here */
+    if (SHARD)
+        for (int i = cta; i < n; i += gridDim.x) {
+            if (s_prefix[i + 1] != s_prefix[i]) continue;
+            for (int hl = 0; hl < G; hl++) {
+                const int seg = i * G + hl;
+                if (tid < 256) {
+                    const int h = (tid >> 5) & 7, d4 = (tid & 31) * 4;
+                    shard_fold_args fa;
+                    fa.rec0 = a.gathered + ((size_t)seg * 8 + h) * kShardLines; fa.rank_stride = (size_t)n * G * 8 * kShardLines; fa.err = a.err;
+                    fa.out = a.out + (size_t)i * a.out_stride + ((size_t)(cache.kv_head_begin + hl) * 8 + h) * HY3A_D + d4;
+                    fa.n_ranks = a.n_dest; fa.my_rank = a.my_rank; fa.line_a = 1 + (d4 >> 1); fa.flag = a.shard_round[seg] + 1u; fa.stage = reinterpret_cast<const uint4 *>(s_dyn); fa.h = h; fa.lane = lane;
+                    fa.own_m = -INFINITY; fa.own_l = 0.f; fa.own_acc[0] = fa.own_acc[1] = fa.own_acc[2] = fa.own_acc[3] = 0.f;
+                    shard_fold(fa);
+                }
+                consumer_sync();
+                if (tid == 0) a.shard_round[seg] += 1u;
+            }
+        }
 }
 
 /* Merge kernel for cross-GPU partials: grid (n_rows*n_heads), block 32; lane -> 4 dims. */
@@ -926,15 +1110,17 @@ template <int DT>
 static cudaError_t launch_decode_dt(hy3a_ctx *ctx, const hy3a_cache_view &cv, const hy3a_batch_view &bv, decode_args &a) {
     const size_t prefix = ((size_t)(ctx->batch_n + 1) * sizeof(int) + 127) & ~(size_t)127;
     dim3 grid(ctx->decode_ctas);
-    static bool attr_set[3][2] = {{false, false}, {false, false}, {false, false}};
+    static bool attr_set[3][3] = {{false, false, false}, {false, false, false}, {false, false, false}};
     a.prefix_bytes = (int)prefix;
     if (ctx->decode_stages >= 2) {
         a.stages = ctx->decode_stages;
         const size_t smem = kFixed + prefix + 128 + (size_t)a.stages * ctx->geom.page_bytes;
-        if (!attr_set[DT][1]) {
-            cudaError_t e = cudaFuncSetAttribute(hy3a_decode_kernel<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        const bool shard = a.n_dest > 0;
+        if (!attr_set[DT][shard ? 2 : 1]) {
+            cudaError_t e = shard ? cudaFuncSetAttribute(hy3a_decode_kernel<DT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax)
+                                  : cudaFuncSetAttribute(hy3a_decode_kernel<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
             if (e != cudaSuccess) return e;
-            attr_set[DT][1] = true;
+            attr_set[DT][shard ? 2 : 1] = true;
         }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid; cfg.blockDim = dim3(kThreads + 32); cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
@@ -942,6 +1128,7 @@ static cudaError_t launch_decode_dt(hy3a_ctx *ctx, const hy3a_cache_view &cv, co
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+        if (shard) return cudaLaunchKernelEx(&cfg, hy3a_decode_kernel<DT, true, true>, cv, bv, a);
         return cudaLaunchKernelEx(&cfg, hy3a_decode_kernel<DT, true>, cv, bv, a);
     } else {
         a.stages = 0;
@@ -973,6 +1160,15 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
     a.scratch = ctx->d_partials; a.counters = ctx->d_counters; a.err = ctx->d_err; a.layer = layer;
     a.trace = ctx->d_trace;
     a.early_prefetch = ctx->use_pdl && !ctx->bulk_write_pending;
+    if (ctx->shard_slot >= 0) {   /* set by hy3a_decode_step_sharded around this call */
+        const int W = ctx->shard_world, slot = ctx->shard_slot;
+        const size_t n_seg = (size_t)ctx->shard_rows * ctx->cfg.kv_head_count;
+        const size_t slice = n_seg * 8 * (HY3A_PARTIAL_FLOATS / 2);    /* 16-byte lines per rank and slot */
+        a.n_dest = W; a.my_rank = ctx->shard_rank;
+        for (int r = 0; r < W; r++) a.dest[r] = reinterpret_cast<uint4 *>(ctx->shard_peer[r]) + ((size_t)slot * W + ctx->shard_rank) * slice;
+        a.gathered = reinterpret_cast<const uint4 *>(ctx->shard_local) + (size_t)slot * W * slice;
+        a.shard_round = reinterpret_cast<unsigned *>(ctx->shard_local + ctx->shard_state_off) + (size_t)slot * n_seg;
+    }
     if (step) {
         a.fused = 1;
         a.q_in = step->q_in; a.k_in = step->k_in; a.v_in = step->v_in;
@@ -1059,6 +1255,7 @@ extern "C" int hy3a_debug_read_trace(hy3a_ctx *ctx, unsigned long long *out, int
     HY3A_CUDA(ctx, cudaMemcpy(out, ctx->d_trace, (size_t)n_ctas * 64 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     return HY3A_OK;
 }
+
 
 int hy3a_launch_merge(hy3a_ctx *ctx, const float *partials, int n_parts, int n_rows, int n_heads, float *out, size_t out_stride) {
     hy3a_merge_kernel<<<n_rows * n_heads, 32, 0, ctx->stream>>>(partials, n_parts, n_rows, n_heads, out, out_stride);

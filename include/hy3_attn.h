@@ -179,6 +179,34 @@ int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, size_t q_strid
 int hy3a_merge_partials(hy3a_ctx *ctx, const float *partials, int n_parts, int n_rows, int n_heads, float *out,
                         size_t out_stride);
 
+/* ---- sequence sharding with the exchange fused into the decode kernel (peer memory over NVLink) ----
+ * New functionality (the reference is single-GPU).  Rank r of `world` processes (one per GPU of one
+ * box, world <= 8) holds a contiguous token range of every sequence.  hy3a_shard_init allocates this
+ * rank's gather buffer ([n_slots][world][n_rows*heads] records of 65 flagged 16-byte lines) and returns its 64-byte CUDA IPC handle; the caller exchanges the handles (any
+ * transport) and passes all of them, in rank order, to hy3a_shard_connect.
+ *
+ * hy3a_decode_step_sharded is hy3a_decode_step over this rank's tokens (k_in = v_in = NULL on ranks that
+ * do not own the tail of the sequences) whose epilogue IS the collective: the CTA that completes a
+ * (row, KV head) stores the rank's {m, l, acc} records straight into every other rank's gather buffer
+ * through the peer mappings, as 16-byte lines that carry their own validity flag (no fence, no separate
+ * signal), polls the lines the other ranks store into its own buffer, folds all records in rank order
+ * (identical bits on all ranks) and writes the final attention output -- one launch per layer, no
+ * second kernel, no NCCL call.  The
+ * wait is bounded (about one second; hy3a_sync then reports HY3A_ETIMEOUT and the context stays usable).
+ * All ranks must launch the same (layer, slot) sequence.  A slot may be reused once every rank has
+ * finished the call that used it: two slots suffice when layer l+1's query depends on layer l's output;
+ * callers that run independent layers back to back use one slot per layer.
+ * hy3a_shard_connect_local replaces the missing ranks by silent stand-in buffers in this process (for
+ * bring-up and for testing the bounded wait on one GPU: with world > 1 every wait runs out).
+ * Teardown: every rank calls hy3a_shard_disconnect (unmaps the peers' buffers; enqueues nothing), the
+ * ranks meet at a barrier of their own, then hy3a_destroy frees the local buffer.                     */
+int hy3a_shard_init(hy3a_ctx *ctx, int rank, int world, int n_slots, int n_rows, unsigned char *handle_out /*[64]*/);
+int hy3a_shard_connect(hy3a_ctx *ctx, const unsigned char *handles /*[world][64]*/);
+int hy3a_shard_connect_local(hy3a_ctx *ctx);
+int hy3a_shard_disconnect(hy3a_ctx *ctx);
+int hy3a_decode_step_sharded(hy3a_ctx *ctx, int layer, int slot, const float *q_in, size_t q_stride, const float *k_in,
+                             size_t k_stride, const float *v_in, size_t v_stride, float *out, size_t out_stride);
+
 /* Causal chunk attention on tcgen05 tensor cores: query i (global index base_slot + i)
  * of sequence seq attends keys [0, base_slot + i]; the chunk's own K/V must already have
  * been appended (the reference does the same, hy3_gpu.cu:823-832).  Replaces
