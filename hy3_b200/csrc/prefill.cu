@@ -124,8 +124,8 @@ __global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cac
             } else {
                 const float s = __half2float(ks[tok]);
                 float f[8];
-                if (DT == 1) {
-                    const uint2 w = *reinterpret_cast<const uint2 *>(page + hy3a_k_dim_off<1>(tok, d));
+                if (DT == 1 || DT == 3) {
+                    const uint2 w = *reinterpret_cast<const uint2 *>(page + (DT == 3 ? hy3a_t_off(tok, d) : hy3a_k_dim_off<1>(tok, d)));
                     const unsigned ww[2] = {w.x, w.y};
 #pragma unroll
                     for (int i = 0; i < 8; i++) f[i] = (float)(signed char)((ww[i >> 2] >> (8 * (i & 3))) & 0xFF) * s;
@@ -151,6 +151,8 @@ __global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cac
             if (t < ntok) {
                 if (DT == 0) {
                     v = __half2float(*reinterpret_cast<const __half *>(page + g.v_off + hy3a_v16_dim_off(tok, d)));
+                } else if (DT == 3) {
+                    v = (float)(signed char)page[g.v_off + hy3a_t_off(d, tok)] * __half2float(vs[tok]);
                 } else if (DT == 1) {
                     const int b = page[g.v_off + hy3a_v_unit_off<1>(tok, d & ~1) + (d & 1)];
                     v = (float)(b - 128) * __half2float(vs[tok]);
@@ -429,7 +431,8 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
     }
     hy3a_cache_view cv = hy3a_view(ctx);
     dim3 g1(pages, kvh);
-    switch (ctx->cfg.kv_dtype) {
+    switch (ctx->geom.dtype) {
+        case 3: hy3a_kv_to_f16_kernel<3><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
         case 0: hy3a_kv_to_f16_kernel<0><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
         case 1: hy3a_kv_to_f16_kernel<1><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
         default: hy3a_kv_to_f16_kernel<2><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;

@@ -26,7 +26,8 @@ __device__ __forceinline__ uint8_t *page_ptr(const hy3a_cache_view &c, int seq, 
  * store them as row `tok` (0..127) of the page.  is_v selects the V area / pair layout.
  * Returns the fp16 scale bits (0 for FP16 caches).                                    */
 template <int DT>
-__device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g, int tok, bool is_v, const float y[4], int d0, int lane) {
+__device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g, int tok, bool is_v, const float y[4], int d0, int lane,
+                                              uint8_t *scale_page = nullptr /* where the scale goes, if not into `page` (a shared-memory copy split in two) */) {
     if (DT == 0) {
         __half2 h01 = __floats2half2_rn(y[0], y[1]);
         __half2 h23 = __floats2half2_rn(y[2], y[3]);
@@ -40,7 +41,7 @@ __device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g,
     float m = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const float qmax = (DT == 1) ? 127.f : 7.f;
+    const float qmax = (DT == 1 || DT == 3) ? 127.f : 7.f;
     float s = __fadd_rn(__fdiv_rn(m, qmax), 1e-8f);
     float inv = __fdiv_rn(1.f, s);
     int c[4];
@@ -48,8 +49,16 @@ __device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g,
     for (int j = 0; j < 4; j++) c[j] = (int)roundf(fmaxf(-qmax, fminf(qmax, __fmul_rn(y[j], inv))));
     __half sh = __float2half(s);
     unsigned sbits = (unsigned)__half_as_ushort(sh);
-    if (lane == 0) *reinterpret_cast<unsigned short *>(page + (is_v ? g.vs_off : g.ks_off) + tok * 2) = (unsigned short)sbits;
-    if (DT == 1) {
+    if (lane == 0) *reinterpret_cast<unsigned short *>((scale_page ? scale_page : page) + (is_v ? g.vs_off : g.ks_off) + tok * 2) = (unsigned short)sbits;
+    if (DT == 3) {
+        if (!is_v) {
+            unsigned w = (unsigned)(c[0] & 0xFF) | ((unsigned)(c[1] & 0xFF) << 8) | ((unsigned)(c[2] & 0xFF) << 16) | ((unsigned)(c[3] & 0xFF) << 24);
+            *reinterpret_cast<unsigned *>(page + hy3a_t_off(tok, d0)) = w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) page[g.v_off + hy3a_t_off(d0 + j, tok)] = (uint8_t)(c[j] & 0xFF);
+        }
+    } else if (DT == 1) {
         if (!is_v) {
             unsigned w = (unsigned)(c[0] & 0xFF) | ((unsigned)(c[1] & 0xFF) << 8) | ((unsigned)(c[2] & 0xFF) << 16) | ((unsigned)(c[3] & 0xFF) << 24);
             *reinterpret_cast<unsigned *>(page + hy3a_k_dim_off<1>(tok, d0)) = w;
