@@ -87,6 +87,11 @@ __device__ __forceinline__ void umma_f16(unsigned d_tmem, unsigned long long a_d
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
 }
+/* A operand in tensor memory (lane = row, 32-bit column c holds elements 2c and 2c+1 of the row's K slice) */
+__device__ __forceinline__ void umma_f16_ta(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -176,7 +181,7 @@ struct prefill_args {
 
 /* ---- pass 2: the attention kernel -------------------------------------------------------------- */
 __global__ void __launch_bounds__(kPfThreads, 1)
-hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
+hy3a_prefill_kernel_v1(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
     extern __shared__ uint8_t s_raw[];
     uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~(uintptr_t)1023);
     const unsigned sbase = smem_u32(sm);
@@ -384,6 +389,230 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #undef BAR
 }
 
+/* ---- pass 2, second generation: two Q tiles per CTA and P in tensor memory ---------------------------------------
+ * One CTA = 32 query tokens x the 8 query heads of one KV head = two 128-row Q tiles, A and B, that share every K/V
+ * tile.  Each tile has its own softmax warpgroup (warps 0-3: A, 4-7: B), its own S (128 TMEM columns) and its own
+ * O (128 columns): 512 columns in all.  While warpgroup A runs the softmax of its S_j, the tensor core computes
+ * S_j of tile B, then P_A.V_j and S_A for tile j+1, and so on: the softmax of one tile hides behind the MMAs of the
+ * other.  P never touches shared memory: the softmax threads write it as packed fp16 pairs over the first 64 columns
+ * of their S (tcgen05.st) and P.V reads its A operand from tensor memory.  That frees 64 KB of shared memory, which
+ * keeps K and V double-buffered beside the two Q tiles.                                                         */
+constexpr int kQTok2 = 32;                     /* query tokens per CTA = two tiles of kQTok */
+constexpr int kPf2SmWarps = 16;                /* softmax warps: tile x = warps with (warp / 4) % 2 == x; column half = warp / 8 */
+constexpr int kPf2Threads = 32 * kPf2SmWarps + 64;   /* + warp 16 = TMA producer, warp 17 = MMA issuer */
+constexpr int kOff2Q = 0, kOff2K = kOff2Q + 2 * kTileBytes, kOff2V = kOff2K + 2 * kTileBytes, kOff2Bar = kOff2V + 2 * kTileBytes;
+constexpr int kOff2Xch = kOff2Bar + 256;        /* float [2 tiles][2 halves][128 rows]: row maxima / denominators exchanged between the two halves */
+constexpr int kPf2Smem = kOff2Xch + 4096 + 1024;   /* maxima in the first 2 KB, denominators in the second */
+enum { B2_Q = 0, B2_KF = 1, B2_VF = 3, B2_KE = 5, B2_VE = 7, B2_SF = 9, B2_P = 11, B2_O = 13 };   /* [2] each except Q */
+
+__global__ void __launch_bounds__(kPf2Threads, 1)
+hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
+    extern __shared__ uint8_t s_raw[];
+    uint8_t *sm = s_raw + ((1024u - (smem_u32(s_raw) & 1023u)) & 1023u);
+    const unsigned sbase = smem_u32(sm);
+    const unsigned bar0 = sbase + kOff2Bar;
+    volatile unsigned *s_tmem = reinterpret_cast<volatile unsigned *>(sm + kOff2Bar + 128);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kOff2Bar + 132);
+#define BAR(i) (bar0 + 8u * (unsigned)(i))
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q0 = blockIdx.x * kQTok2, hl = blockIdx.y;
+    const int kv_end = min(a.base + q0 + kQTok2, a.base + a.nq);   /* keys [0, kv_end) matter for this CTA */
+    const int ntiles = (kv_end + kKeys - 1) / kKeys;
+
+    if (tid == 0) {
+        *s_abort = 0;
+        mbar_init(BAR(B2_Q), 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(BAR(B2_KF + i), 1); mbar_init(BAR(B2_VF + i), 1); mbar_init(BAR(B2_KE + i), 1); mbar_init(BAR(B2_VE + i), 1);
+            mbar_init(BAR(B2_SF + i), 1); mbar_init(BAR(B2_P + i), 256); mbar_init(BAR(B2_O + i), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {   /* one warp allocates all 512 TMEM columns (1 CTA per SM) */
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + kOff2Bar + 128), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = *s_tmem;
+    /* tile x: S at columns 128x (P over its first 64 columns), O at columns 256 + 128x */
+
+    if (warp == kPf2SmWarps) {
+        /* ===================== TMA producer ===================== */
+        if (lane == 0) {
+            mbar_expect_tx(BAR(B2_Q), 2 * kTileBytes);
+            for (int x = 0; x < 2; x++) {
+                tma_load_3d(sbase + kOff2Q + x * kTileBytes, &tm_q, BAR(B2_Q), 0, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
+                tma_load_3d(sbase + kOff2Q + x * kTileBytes + 16384, &tm_q, BAR(B2_Q), 64, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
+            }
+            for (int j = 0; j < ntiles; j++) {
+                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
+                if (!mbar_wait(BAR(B2_KE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
+                mbar_expect_tx(BAR(B2_KF + st), kTileBytes);
+                tma_load_3d(sbase + kOff2K + st * kTileBytes, &tm_k, BAR(B2_KF + st), 0, j * kKeys, hl);
+                tma_load_3d(sbase + kOff2K + st * kTileBytes + 16384, &tm_k, BAR(B2_KF + st), 64, j * kKeys, hl);
+                if (!mbar_wait(BAR(B2_VE + st), ph ^ 1u, s_abort, a.err, 11u)) break;
+                mbar_expect_tx(BAR(B2_VF + st), kTileBytes);
+                tma_load_3d(sbase + kOff2V + st * kTileBytes, &tm_v, BAR(B2_VF + st), j * kKeys, 0, hl);
+                tma_load_3d(sbase + kOff2V + st * kTileBytes + 16384, &tm_v, BAR(B2_VF + st), j * kKeys + 64, 0, hl);
+            }
+        }
+    } else if (warp == kPf2SmWarps + 1) {
+        /* ===================== MMA issuer =====================
+         * order: S_A(0) S_B(0) | PV_A(0) S_A(1) | PV_B(0) S_B(1) | PV_A(1) S_A(2) | ...
+         * S_x(j+1) overwrites the columns P_x(j) lives in, so it is issued behind PV_x(j) (the tensor core runs in order) */
+        if (lane == 0) {
+            bool ok = mbar_wait(BAR(B2_Q), 0u, s_abort, a.err, 20u);
+            auto issue_qk = [&](int x, int j) {      /* S_x(j) = Q_x . K_j^T : 8 k-steps of 16 over d = 128 */
+                const int st = j & 1;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    const unsigned off = (unsigned)(kk >> 2) * 16384u + (unsigned)(kk & 3) * 32u;
+                    umma_f16(tmem + 128u * x, make_desc(sbase + kOff2Q + x * kTileBytes + off), make_desc(sbase + kOff2K + st * kTileBytes + off), kk > 0);
+                }
+                umma_commit(BAR(B2_SF + x));
+            };
+            if (ok) ok = mbar_wait(BAR(B2_KF), 0u, s_abort, a.err, 21u);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_qk(0, 0);
+                issue_qk(1, 0);
+                umma_commit(BAR(B2_KE));
+            }
+            for (int j = 0; j < ntiles && ok; j++) {
+                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
+                const int st1 = (j + 1) & 1; const unsigned ph1 = (unsigned)((j + 1) >> 1) & 1u;
+                for (int x = 0; x < 2 && ok; x++) {
+                    if (x == 0) ok = mbar_wait(BAR(B2_VF + st), ph, s_abort, a.err, 23u);
+                    if (ok) ok = mbar_wait(BAR(B2_P + x), (unsigned)j & 1u, s_abort, a.err, 24u);   /* P_x(j) in tensor memory, O_x rescaled */
+                    if (ok && j + 1 < ntiles && x == 0) ok = mbar_wait(BAR(B2_KF + st1), ph1, s_abort, a.err, 25u);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    /* O_x += P_x(j) . V_j : 8 k-steps of 16 keys; A = 8 columns of packed fp16 pairs per step */
+#pragma unroll
+                    for (int kk = 0; kk < 8; kk++) {
+                        const unsigned off = (unsigned)(kk >> 2) * 16384u + (unsigned)(kk & 3) * 32u;
+                        umma_f16_ta(tmem + 256u + 128u * x, tmem + 128u * x + 8u * kk, make_desc(sbase + kOff2V + st * kTileBytes + off), (j > 0 || kk > 0));
+                    }
+                    umma_commit(BAR(B2_O + x));
+                    if (x == 1) umma_commit(BAR(B2_VE + st));
+                    if (j + 1 < ntiles) {
+                        issue_qk(x, j + 1);
+                        if (x == 1) umma_commit(BAR(B2_KE + st1));
+                    }
+                }
+            }
+        }
+    } else {
+        /* ===================== softmax warps: tile x = (warp / 4) % 2, column half hf = warp / 8; thread = (row of Q
+         * tile x, 64 of its 128 key columns).  The two threads of a row exchange their maxima through shared memory. */
+        const int x = (warp >> 2) & 1, hf = warp >> 3, r = tid & 127, t_local = r >> 3, h = r & 7;
+        const int tq0 = q0 + x * kQTok;                          /* first query token of this tile */
+        const int qpos = a.base + tq0 + t_local;                 /* global index of this row's query */
+        const bool row_valid = (tq0 + t_local) < a.nq;
+        const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16; /* this warp's quarter of the TMEM lanes */
+        const unsigned tm_s = tmem + 128u * x, tm_o = tmem + 256u + 128u * x;
+        float *xch = reinterpret_cast<float *>(sm + kOff2Xch) + x * 256;   /* [2 halves][128 rows] */
+        float m = -INFINITY, l = 0.f;    /* l: this thread's half of the row's denominator */
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; j++) {
+            ok = __all_sync(0xffffffffu, mbar_wait(BAR(B2_SF + x), (unsigned)j & 1u, s_abort, a.err, 30u));   /* keep the warp together */
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int k0 = j * kKeys + 64 * hf;                    /* first key of this thread's columns */
+            const bool masked = (j * kKeys + kKeys - 1 > a.base + tq0);   /* the tile crosses the diagonal of some row */
+            unsigned v0[32], v1[32];
+            tmem_ld32(tm_s + lane_base + 64u * hf, v0);
+            tmem_ld32(tm_s + lane_base + 64u * hf + 32u, v1);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                float s0 = __uint_as_float(v0[i]) * kScaleLog2, s1 = __uint_as_float(v1[i]) * kScaleLog2;
+                if (masked && k0 + i > qpos) s0 = -INFINITY;
+                if (masked && k0 + 32 + i > qpos) s1 = -INFINITY;
+                v0[i] = __float_as_uint(s0); v1[i] = __float_as_uint(s1);
+                mx = fmaxf(mx, fmaxf(s0, s1));
+            }
+            xch[hf * 128 + r] = mx;
+            asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
+            mx = fmaxf(mx, xch[(hf ^ 1) * 128 + r]);
+            const bool grow = mx > m + kPfThreshold;              /* true while m == -inf (key 0 is never masked) */
+            const float m_new = grow ? mx : m;
+            unsigned pk[32];
+            float lsum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const unsigned p0 = pack_h2(ex2f(__uint_as_float(v0[i]) - m_new), ex2f(__uint_as_float(v0[i + 1]) - m_new));
+                const unsigned p1 = pack_h2(ex2f(__uint_as_float(v1[i]) - m_new), ex2f(__uint_as_float(v1[i + 1]) - m_new));
+                pk[i >> 1] = p0; pk[16 + (i >> 1)] = p1;
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&p0)), f1 = __half22float2(*reinterpret_cast<const __half2 *>(&p1));
+                lsum += (f0.x + f0.y) + (f1.x + f1.y);
+            }
+            /* O_x is only ours again when P_x(j-1).V_(j-1) has completed */
+            if (j > 0 && ok) {
+                ok = __all_sync(0xffffffffu, mbar_wait(BAR(B2_O + x), (unsigned)(j - 1) & 1u, s_abort, a.err, 31u));
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            /* tcgen05.ld / .st are warp-collective: the whole warp rescales its 32 rows (this thread: 64 of the 128 output
+             * dims) as soon as one of them moved its reference (the others multiply by exactly 1) */
+            const float alpha = grow ? ex2f(m - m_new) : 1.f;     /* 0 on the first tile (m = -inf) */
+            if (__any_sync(0xffffffffu, grow)) {
+                l *= alpha;
+                if (j > 0) {
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        unsigned v[32];
+                        tmem_ld32(tm_o + lane_base + 64u * hf + 32u * c, v);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tmem_st32(tm_o + lane_base + 64u * hf + 32u * c, v);
+                    }
+                }
+                m = m_new;
+            }
+            l += lsum;
+            /* P over the first 64 columns of S (column c = keys 2c, 2c+1): this thread's 64 keys are columns 32 hf .. 32 hf + 31.
+             * Both halves have read their S columns (the barrier above), so the overwrite is safe. */
+            tmem_st32(tm_s + lane_base + 32u * hf, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(BAR(B2_P + x));
+        }
+        /* epilogue: O / l, l = sum of the two halves */
+        xch[512 + hf * 128 + r] = l;
+        asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
+        l += xch[512 + (hf ^ 1) * 128 + r];
+        if (ok && ntiles > 0) ok = mbar_wait(BAR(B2_O + x), (unsigned)(ntiles - 1) & 1u, s_abort, a.err, 32u);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__all_sync(0xffffffffu, ok) && ntiles > 0) {      /* warp-uniform: tcgen05.ld is warp-collective */
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float *orow = a.out + (size_t)(tq0 + t_local) * a.out_stride + (size_t)((a.kv_head_begin + hl) * 8 + h) * HY3A_D + 64 * hf;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                unsigned v[32];
+                tmem_ld32(tm_o + lane_base + 64u * hf + 32u * c, v);
+                if (row_valid)
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4 *>(orow + 32 * c + i) = make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
+                                                                                   __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            }
+        }
+    }
+    /* ---- common exit: everybody arrives here, also after a wait ran out; release TMEM */
+    if (*s_abort && warp == kPf2SmWarps && lane == 0) {
+        /* copies already issued must land before the shared memory goes away */
+        for (int st = 0; st < 2; st++)
+            for (unsigned ph = 0; ph < 2; ph++)
+                for (unsigned spin = 0; spin < (1u << 12) && !mbar_test(BAR(B2_KF + st), ph) && !mbar_test(BAR(B2_VF + st), ph); spin++) __nanosleep(64);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+#undef BAR
+}
+
 } /* namespace */
 
 typedef CUresult (*hy3a_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -458,13 +687,20 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
     }
     static bool attr_set = false;
     if (!attr_set) {
-        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel_v1, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPf2Smem));
         attr_set = true;
     }
     prefill_args a;
     a.out = out; a.out_stride = out_stride; a.base = base_slot; a.nq = nq; a.kv_head_begin = ctx->cfg.kv_head_begin; a.err = ctx->d_err;
-    dim3 g2((nq + kQTok - 1) / kQTok, kvh);
-    hy3a_prefill_kernel<<<g2, kPfThreads, kPfSmem, ctx->stream>>>(tq, tk, tv, a);
+    const char *v1 = getenv("HY3A_PF_V1");   /* first-generation kernel: one Q tile per CTA, P through shared memory */
+    if (v1 && atoi(v1)) {
+        dim3 g2((nq + kQTok - 1) / kQTok, kvh);
+        hy3a_prefill_kernel_v1<<<g2, kPfThreads, kPfSmem, ctx->stream>>>(tq, tk, tv, a);
+    } else {
+        dim3 g2((nq + kQTok2 - 1) / kQTok2, kvh);
+        hy3a_prefill_kernel<<<g2, kPf2Threads, kPf2Smem, ctx->stream>>>(tq, tk, tv, a);
+    }
     ctx->launches++;
     ctx->bulk_write_pending = 1;
     HY3A_CUDA(ctx, cudaGetLastError());
