@@ -12,7 +12,12 @@ Metric: decode attention KV GB/s = algorithmic KV bytes read per step (ntok x 20
 i.e. codes + fp16 scales of K and V) / time.  Synthetic seeded N(0,1) data, random "weights".
 
 N>1 (weak scaling): every rank holds 32768 positions per layer of ONE sequence of 32768*N tokens
-(sequence sharding); per layer each rank emits {m,l,acc} partials, one NCCL all-gather, local merge.
+(sequence sharding); per layer ONE launch per rank: the decode kernel's epilogue stores the rank's {m,l,acc}
+records into every rank's gather buffer over NVLink peer memory, waits for the others' and folds them
+(--nccl-exchange: partial records, NCCL all-gather, merge kernel instead).
+
+Secondary objects in the same JSON line (N=1): "prefill" (configs[2], tensor roofline), "ragged_batch" (configs[4] on one
+GPU) and "long_context_int4" (configs[3] on one GPU).
 
 --impl reference: the reference engine's own CPU attention() (hy3.c:617-652, compiled from the
 reference sources into oracle/_ref; falls back to the C restatement in oracle/) on the host cores.
@@ -157,6 +162,61 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------- GPU arm
+def batch_section(torch, dev, kind):
+    """Secondary decode workloads, one layer each, device-timed back-to-back fused steps:
+    'ragged'  -- configs[4] on one GPU: 64 sequences, lengths 1024 + (rng % 64513) (seeded), INT8 KV, one token per
+                 sequence per step (all 8 KV heads on this GPU);
+    'long'    -- configs[3] on one GPU: batch 1, INT4 KV, 262 144 positions, YaRN factor 4 (attn_factor on q and k)."""
+    import numpy as np
+    from hy3_b200 import Hy3Attn
+    rng = np.random.default_rng(SEED)
+    if kind == "ragged":
+        kv, lens = "int8", [int(1024 + rng.integers(0, 64513)) for _ in range(64)]
+        what = "configs[4]: 64 sequences, lengths uniform in [1024, 65536] (seeded), INT8 KV, 1 layer, all 8 KV heads on one GPU"
+    else:
+        kv, lens = "int4", [262144]
+        what = "configs[3]: batch 1, INT4 KV, 262144 positions, YaRN factor 4, 1 layer, unsharded"
+    B = len(lens)
+    steps = 24
+    ctx = Hy3Attn(kv_dtype=kv, n_layers=1, max_seqs=B, max_batch=B, max_tokens=sum(lens) + (steps + 129) * B, max_tokens_per_seq=max(lens) + steps + 129, device=dev.index)
+    if kind == "long":
+        inv = (1.0 / (11158840.0 ** (np.arange(64) / 64.0))).astype(np.float32)
+        ctx.set_rope(inv / 4.0, 1.0 + 0.1 * np.log(4.0))      # every frequency interpolated: the speed does not depend on the blend
+    for i, n in enumerate(lens):
+        ctx.fill_random(0, i, 0, n, SEED + i)
+    q = torch.randn((B, H, D), device=dev)
+    k = torch.randn((B, G, D), device=dev)
+    v = torch.randn((B, G, D), device=dev)
+    out = torch.zeros((B, H, D), device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    t = 0
+    for _ in range(4):                                          # warm-up
+        ctx.batch_set(list(range(B)), [n + t for n in lens]); ctx.decode_step(0, q, k, v, out=out); t += 1
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(steps - 4):
+        ctx.batch_set(list(range(B)), [n + t for n in lens])
+        ev[0].record(torch.cuda.current_stream(dev))
+        ctx.decode_step(0, q, k, v, out=out)
+        ev[1].record(torch.cuda.current_stream(dev))
+        ev[1].synchronize()
+        times.append(ev[0].elapsed_time(ev[1]))
+        t += 1
+    ctx.sync()
+    ctx.close()
+    ms = statistics.median(times)
+    per_tok = {"int8": 2080, "int4": 1056, "fp16": 4096}[kv]
+    nbytes = (sum(lens) + B * (4 + (steps - 4) // 2)) * per_tok
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = json.load(open(p))["hbm_gbs"] if os.path.exists(p) else 6650.0
+    gbs = nbytes / ms / 1e6
+    return {"metric": METRIC, "value": gbs, "unit": UNIT, "workload": what, "ms_per_launch": ms, "algorithmic_bytes_per_launch": nbytes,
+            "l2": "%.2f GB streamed per launch, far beyond L2" % (nbytes / 1e9),
+            "roofline": {"bound": "hbm", "kernel": "hy3a_decode_kernel<%s>" % kv, "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                         "frac_of_nominal_8TBs": gbs / 8000.0,
+                         "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if os.path.exists(p) else "fallback 6.65 TB/s"}}
+
+
 def prefill_section(torch, dev, kv="fp16", prompt=8192, chunk=512):
     """Secondary metric: chunked causal prefill attention, an 8192-token prompt in 512-token chunks,
     FP16 KV cache, 64 Q / 8 KV heads, one layer (configs[2]).  TFLOP/s = 4*128*64*sum(pos+1) / device time
@@ -396,6 +456,10 @@ def run_ours(args):
         roofline["traffic_source"] = t["source"]
     ctx.sync()
     prefill = prefill_section(torch, dev) if (rank == 0 and world == 1 and not args.no_prefill) else None
+    extra = {}
+    if rank == 0 and world == 1 and not args.no_prefill:
+        for kind in ("ragged", "long"):
+            extra[kind] = batch_section(torch, dev, kind)
     clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
@@ -416,7 +480,8 @@ def run_ours(args):
                 "frac_of_hbm_peak": value / world / peak, "roofline": roofline, "cpu_baseline": cpu,
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_in.numel() * 4,
                         "d2h_bytes_per_step": host_out.numel() * 4},
-                "gpu_launches": per_step_launches * args.steps, "clocks": clocks, "prefill": prefill}
+                "gpu_launches": per_step_launches * args.steps, "clocks": clocks, "prefill": prefill,
+                "ragged_batch": extra.get("ragged"), "long_context_int4": extra.get("long")}
         print(json.dumps(line), flush=True)
     if world > 1:
         # tearing the NCCL communicator down while a captured graph still references it can stall;
@@ -445,6 +510,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the secondary chunked-prefill measurement")
     ap.add_argument("--prefill-only", action="store_true", help="run only the chunked-prefill measurement and print its JSON object")
+    ap.add_argument("--batch-only", choices=["ragged", "long"], help="run only one of the secondary decode workloads and print its JSON object")
     ap.add_argument("--prefill-prompt", type=int, default=8192)
     ap.add_argument("--prefill-kv", default="fp16", choices=["int8", "int4", "fp16"])
     ap.add_argument("--nccl-exchange", action="store_true", help="N>1: exchange the partial records with an NCCL all-gather instead of peer-memory stores from the kernel")
@@ -457,6 +523,10 @@ def main():
         import torch
         torch.cuda.set_device(0)
         print(json.dumps(prefill_section(torch, torch.device("cuda", 0), kv=args.prefill_kv, prompt=args.prefill_prompt)))
+    elif args.batch_only:
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps(batch_section(torch, torch.device("cuda", 0), args.batch_only)))
     elif args.impl == "reference":
         run_reference(args)
     else:

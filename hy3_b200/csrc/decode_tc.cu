@@ -5,9 +5,8 @@
  * Same job as decode.cu (replaces attention_split_kv_kernel + attention_reduce_kernel,
  * hy3_gpu.cu:183-247), same schedule, same records, same merge; what changes is who does the
  * arithmetic.  In decode.cu every warp builds mma.sync fragments from the page, converts V codes
- * to fp16 and runs softmax on 16-token granules: about 3 800 warp instructions per 128-token page,
- * which makes the INT8 kernel issue/latency-bound at about 1.0 us per page per SM while HBM could
- * deliver a page every 0.76 us.  Here the page that the bulk copy lands in shared memory IS the
+ * to fp16 and runs softmax on 16-token granules: about 3 800 warp instructions per 128-token page
+ * (INT4 more: that variant is compute-bound).  Here the page that the bulk copy lands in shared memory IS the
  * tensor-core operand (K tile: 128 tokens x 128 B; V^T tile: 128 dims x 128 B; both in the
  * K-major 128-byte-swizzle order) and the tokens, not the heads, are the M dimension:
  *
@@ -17,27 +16,30 @@
  *   O^T[128 dim x 16]  = V^T[128 x 128] . Pd^T   kind::i8; the 16 columns are the 8 heads x {high, low}
  *                                                digit of w = p * vscale(token) / vscale_max
  *
- * Accumulators live in TMEM (S^T and O^T, double-buffered: 64 columns).  The CUDA cores only do the
- * softmax: thread t of a 128-thread group owns token t of the page (one TMEM lane): 16 integers in,
- * 8 scores, one page-wide max per head (warp redux + 4-warp exchange), 8 exponentials, 16 digit
- * bytes out -- about 600 warp instructions per page.  The same thread then owns output dim t of
- * O^T: it reads 16 integers and adds them to 8 fp32 accumulators (acc is rescaled every page by
- * exp2(m_old - m_new): no lazy threshold is needed, the state is 8 floats).  Two groups alternate
- * pages so that the softmax of page j+1 overlaps the MMAs of page j.
+ * Accumulators live in TMEM (two S^T buffers per group, one O^T per group).  The CUDA cores only do the softmax: a
+ * group of 256 threads owns a page; thread t of each 128-thread half owns token t of the page (one TMEM lane) for 4 of
+ * the 8 query heads: 8 integers in, 4 scores, one page-wide max per head (warp redux + 4-warp exchange), 4
+ * exponentials, 8 digit bytes out.  The same thread then owns output dim t of O^T: 8 integers added to 4 fp32
+ * accumulators (rescaled every page by exp2(m_old - m_new): the state is small, no lazy threshold needed).  The P digits
+ * are sized by the largest V scale of the page's valid tokens.  Two groups alternate pages.
  *
- * Warps: 0-3 softmax group 0, 4-7 group 1 (TMEM lane quadrant = warp % 4), 8 page producer
- * (cp.async.bulk ring, and the fused append of the newest token), 9 MMA issuer (one lane).
- * Every wait is bounded; a wait that runs out raises a CTA-wide abort flag, records a code in the
- * context's error word, every later wait returns at once and the kernel runs to its end; TMEM is
- * always released.  All tcgen05.ld are executed by whole warps under uniform control flow.
+ * Warps: 0-7 softmax group 0, 8-15 group 1 (TMEM lane quadrant = warp % 4); 16 page producer; 17, 18 MMA issuers.
+ *  - producer: two bulk copies per page into two rings (K tile: dead after Q.K^T; V^T + scales: live until P.V), and the
+ *    fused append of the newest token (same arithmetic as the append kernel) into the landed copies and into HBM;
+ *  - issuer of group g (one lane, blocking waits): Q.K^T of the group's next pages two ahead of its softmax, P.V as
+ *    soon as the group's digits are written.  The scalar code around a tcgen05.mma costs more than the MMA (26 ns at
+ *    N = 16 when issued back to back), so one issuer per group runs beside the softmax instead of inside it.
+ * Every wait is bounded; a wait that runs out raises a CTA-wide abort flag, records a code in the context's error
+ * word, every later wait returns at once and the kernel runs to its end; TMEM is always released.  All tcgen05.ld are
+ * executed by whole warps under uniform control flow.  Events that one side can produce twice before the other side
+ * looks (queries of the next segment ready, append done) are monotonic counters, not parity barriers.
  *
  * Roofline: HBM; algorithmic bytes per (token, KV head) = 260.
  *
- * Measured on B200: one lane issues a tcgen05.mma of M = 128, K = 32 bytes every ~75 ns whatever N (16..128) and
- * kind (i8, f16) -- the cost follows the A operand, N rides along.  A page costs 4 + 4 such instructions, i.e.
- * >= 0.6 us of tensor-core time per page and SM against 0.76 us of HBM time, so with tokens as the M dimension this
- * kernel can at best draw level with HBM at batch 1; it is kept as an opt-in path (HY3A_INT8_TC=1).  Batches with
- * several queries per KV head would fill N (16 columns per query) at the same instruction count.
+ * Measured on B200 (INT8, 32 768 positions, batch 1): the stream phase runs at about 0.8 us per page and SM, the same
+ * as decode.cu -- both are bound by HBM and ring depth there -- and the launch takes 22 us in both; what this kernel buys
+ * is CUDA-core headroom (about 1/6 of the instructions).  It is the opt-in path (HY3A_INT8_TC=1) until the head and
+ * tail of the launch, which the two kernels share, are shorter.
  */
 #include <cuda_fp16.h>
 #include <math.h>
@@ -50,10 +52,10 @@
 namespace {
 
 #ifndef HY3A_TC_GROUPS
-#define HY3A_TC_GROUPS 3
+#define HY3A_TC_GROUPS 2
 #endif
 #ifndef HY3A_TC_HALVES
-#define HY3A_TC_HALVES 1
+#define HY3A_TC_HALVES 2
 #endif
 constexpr int kGroups = HY3A_TC_GROUPS;         /* softmax groups; page j of a CTA belongs to group j % kGroups */
 constexpr int kHalves = HY3A_TC_HALVES;         /* a group = kHalves x 128 threads; part k handles kHpt query heads of every token
@@ -62,8 +64,8 @@ constexpr int kHpt = 8 / kHalves;               /* heads per thread */
 constexpr int kGroupThreads = 128 * kHalves;
 constexpr int kSmWarps = 4 * kHalves * kGroups;
 static_assert(kSmWarps >= 8 && kSmWarps <= 30, "warps 0-7 prepare the queries; 1024 threads at most");
-constexpr int kSmThreads = 32 * kSmWarps;       /* the softmax warps; warp kSmWarps = page producer, kSmWarps + 1 = MMA issuer */
-constexpr int kTcThreads = kSmThreads + 64;
+constexpr int kSmThreads = 32 * kSmWarps;       /* the softmax warps; warp kSmWarps = page producer, then one MMA issuer warp per group */
+constexpr int kTcThreads = kSmThreads + 32 + 32 * kGroups;   /* + producer warp + one MMA issuer warp per group */
 /* A page travels as two bulk copies into two rings: the K tile (first 16 KB) is dead as soon as Q.K^T has run, the rest
  * (V^T tile + K scales + V scales) lives until P.V has run -- about a softmax later.  Separate rings let the long-lived
  * parts be many without the short-lived ones taking room. */
@@ -82,13 +84,16 @@ constexpr int kFoldBytes = kGroups * 8 * HY3A_D * 4, kLandBytes = kLandPieces * 
 constexpr int kOffPrefix = kOffLand + (kFoldBytes > kLandBytes ? kFoldBytes : kLandBytes);
 enum { BAR_KFULL = 0, BAR_KEMPTY = 64, BAR_VFULL = 128, BAR_VEMPTY = 192, BAR_SFULL = 256, BAR_SFREE = 320, BAR_PFULL = 384, BAR_OFULL = 416, BAR_OFREE = 448, BAR_QREADY = 480, BAR_APPEND = 488 };
 static_assert(kKStages <= 8 && 2 * kGroups <= 8, "barrier areas hold 8 entries each");
+static_assert(kKStages >= 2 * kGroups + 1, "Q.K^T is issued two of a group's pages ahead: their K tiles must fit the K ring");
 constexpr unsigned kColO = 32u * kGroups;       /* TMEM columns: S^T buffers (group g, page parity b: 16*(2g+b)), then O^T of group g at kColO + 16g */
 constexpr unsigned kTmemCols = 256;
 struct tc_misc {
     unsigned tmem;
     int abort_flag;
     int flag;
-    unsigned vnew;
+    unsigned q_ready;           /* segments whose query digits are in shared memory (monotonic, for the same reason as below) */
+    unsigned appends_done;      /* fused appends completed by the producer warp so far (monotonic; a parity barrier would alias when the
+                                 * producer runs two appends ahead of an issuer in a CTA that walks through many short segments) */
     float qf[8];
     int gmax[kGroups][2][kHalves][4][kHpt + 1];   /* [group][slot][part][warp][head of the part | V scale] */       /* [group][slot][warp][head | 8]: order-preserving ints of the per-warp page maxima of the
                                  * scores of each head and ([8]) of the V scales */
@@ -164,14 +169,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
     if (tid == 0) {
         s_prefix[0] = 0;
         mi.abort_flag = 0;
+        mi.appends_done = 0u;
+        mi.q_ready = 0u;
         for (int i = 0; i < kKStages; i++) { mbar_init(bar_base + BAR_KFULL + 8 * i, 1); mbar_init(bar_base + BAR_KEMPTY + 8 * i, 1); }
         for (int i = 0; i < a.stages; i++) { mbar_init(bar_base + BAR_VFULL + 8 * i, 1); mbar_init(bar_base + BAR_VEMPTY + 8 * i, 1); }
-        for (int b = 0; b < 2 * kGroups; b++) { mbar_init(bar_base + BAR_SFULL + 8 * b, 1); mbar_init(bar_base + BAR_SFREE + 8 * b, kGroupThreads); }
+        for (int b = 0; b < 2 * kGroups; b++) mbar_init(bar_base + BAR_SFULL + 8 * b, 1);
         for (int g2 = 0; g2 < kGroups; g2++) {
-            mbar_init(bar_base + BAR_PFULL + 8 * g2, kGroupThreads); mbar_init(bar_base + BAR_OFULL + 8 * g2, 1); mbar_init(bar_base + BAR_OFREE + 8 * g2, kGroupThreads);
+            mbar_init(bar_base + BAR_OFULL + 8 * g2, 1); mbar_init(bar_base + BAR_PFULL + 8 * g2, kGroupThreads);
         }
-        mbar_init(bar_base + BAR_QREADY, kSmThreads);
-        mbar_init(bar_base + BAR_APPEND, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -230,7 +235,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
     if (idle && !SHARD) return;   /* sharded: idle CTAs may still own the fold of rows without local keys */
 
     /* ---- TMEM: two S^T buffers per group (so that Q.K^T runs ahead of the softmax) and one O^T per group */
-    if (warp == kSmWarps + 1 && !idle) {
+    if (warp == kSmWarps && !idle) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&mi.tmem)), "n"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -333,8 +338,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                     if (lane == 0) atomicMax(cache.vs_max + a.layer * G + sg.hl, sb);
                     fence_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_base + BAR_APPEND);
                     appends++;
+                    if (lane == 0) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&mi.appends_done)), "r"(appends) : "memory");
                 }
             }
             u = sg.seg_u0 + sg.p_end;
@@ -351,81 +356,77 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
             }
         }
         (void)appends;
-    } else if (warp == kSmWarps + 1) {
-        /* ================= MMA issuer: one lane.  Page j of the CTA (ring position) belongs to group j % kGroups.  The
-         * lane polls, without blocking on any single barrier, for the next Q.K^T it may issue (page landed, S^T buffer of
-         * the group free: up to two pages per group ahead of the softmax) and the next P.V (digits written, O^T read),
-         * so the tensor core never waits behind a softmax. */
+    } else if (warp > kSmWarps) {
+        /* ================= MMA issuers: one warp (one lane) per softmax group.  It mirrors the group's walk over the
+         * CTA's pages and issues, with blocking waits: Q.K^T of the group's first two pages of a segment; then, each time
+         * the group has written the digits of page j (and has read S^T(j) and O^T of its previous page), P.V of page j and
+         * Q.K^T of page j + 2 kGroups into the S^T buffer just read.  The scalar code around a tcgen05.mma costs far more
+         * than the MMA itself (about 26 ns at N = 16), so issuing runs beside the softmax, not inside it. */
+        const int group = warp - kSmWarps - 1;
         if (lane == 0 && !idle) {
-            unsigned it = 0, segs = 0, appends = 0;
-            unsigned cq[kGroups], cp[kGroups];
-#pragma unroll
-            for (int g2 = 0; g2 < kGroups; g2++) cq[g2] = cp[g2] = 0u;
+            unsigned it = 0, cnt = 0, segs = 0, appends = 0;
             bool ok = true;
-            const unsigned long long dq = make_desc(s_base + kOffQt);
+            /* wait (bounded, about half a second) until a monotonic counter in shared memory has passed `seen` */
+            auto wait_counter = [&](unsigned *ctr, unsigned seen, unsigned where) {
+                unsigned long long t0 = 0, t1;
+                for (unsigned spin = 0;; spin++) {
+                    unsigned done;
+                    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(done) : "r"(smem_u32(ctr)) : "memory");
+                    if (done > seen) return true;
+                    if ((spin & 15u) == 15u) {
+                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                        if (t0 == 0) t0 = t1;
+                        if (mi.abort_flag || t1 - t0 > 500000000ull) {
+                            mi.abort_flag = 1;
+                            if (atomicCAS(a.err, 0u, 1u) == 0u) a.err[1] = where;
+                            return false;
+                        }
+                        __nanosleep(64);
+                    }
+                }
+            };
+            const unsigned long long dq = make_desc(s_base + kOffQt), dk0 = make_desc(kring), dv0 = make_desc(vring);
+            const unsigned long long dp = make_desc(s_base + kOffPt + 2048u * (unsigned)group);
             for (long long u = u_begin; u < u_end && ok;) {
                 const segment sg = locate(s_prefix, batch, n, G, u, u_end);
                 const int npg = sg.p_end - sg.p_begin;
                 const bool newest_here = a.fused && a.k_in && (sg.p_end - 1 == ((sg.len - 1) >> 7));
-                ok = mbar_wait_blocking(bar_base + BAR_QREADY, segs & 1u, &mi.abort_flag, a.err, 5u);
+                const int j0 = (int)(((unsigned)group - it) % kGroups);
+                auto issue_qk = [&](int jq, unsigned sbuf) {
+                    const unsigned itq = it + (unsigned)jq, kst = itq % (unsigned)kKStages, kph = (itq / (unsigned)kKStages) & 1u;
+                    bool k2 = mbar_wait_blocking(bar_base + BAR_KFULL + 8 * kst, kph, &mi.abort_flag, a.err, 6u);
+                    /* the producer warp has patched the newest token into this page when its counter has passed ours */
+                    if (k2 && newest_here && jq == npg - 1) k2 = wait_counter(&mi.appends_done, appends, 7u);
+                    if (!k2) return false;
+                    fence_after();
+                    const unsigned long long dk = dk0 + (unsigned long long)(kst * (unsigned)(kKBytes >> 4));
+                    const unsigned d = tmem + 16u * sbuf;
+                    umma_i8(d, dk, dq, 0u); umma_i8(d, dk + 2u, dq + 2u, 1u); umma_i8(d, dk + 4u, dq + 4u, 1u); umma_i8(d, dk + 6u, dq + 6u, 1u);
+                    umma_commit(bar_base + BAR_SFULL + 8 * sbuf);
+                    umma_commit(bar_base + BAR_KEMPTY + 8 * kst);   /* the K tile is consumed as soon as these MMAs have run */
+                    if (itq < 8) TRACE(48 + itq);
+                    return true;
+                };
+                ok = wait_counter(&mi.q_ready, segs, 5u);
                 segs++;
-                int qk = 0, pv = 0;
-                unsigned idle_polls = 0;
-                while (ok && pv < npg) {
-                    bool progress = false;
-                    if (qk < npg) {
-                        const unsigned itj = it + (unsigned)qk, kst = itj % (unsigned)kKStages, kph = (itj / (unsigned)kKStages) & 1u, g = itj % kGroups;
-                        unsigned cqg = 0;
-#pragma unroll
-                        for (int g2 = 0; g2 < kGroups; g2++) if ((unsigned)g2 == g) cqg = cq[g2];
-                        const unsigned sb = 2u * g + (cqg & 1u);
-                        const bool newest = newest_here && qk == npg - 1;
-                        if (mbar_test(bar_base + BAR_KFULL + 8 * kst, kph) && mbar_test(bar_base + BAR_SFREE + 8 * sb, ((cqg >> 1) & 1u) ^ 1u) &&
-                            (!newest || mbar_test(bar_base + BAR_APPEND, appends & 1u))) {
-                            if (newest) appends++;
-                            fence_after();
-                            const unsigned long long dk = make_desc(kring + kst * (unsigned)kKBytes);
-#pragma unroll
-                            for (int k = 0; k < 4; k++) umma_i8(tmem + 16u * sb, dk + 2u * k, dq + 2u * k, k > 0 ? 1u : 0u);
-                            umma_commit(bar_base + BAR_SFULL + 8 * sb);
-                            umma_commit(bar_base + BAR_KEMPTY + 8 * kst);   /* the K tile is consumed as soon as these MMAs have run */
-                            if (itj < 8) TRACE(48 + itj);
-#pragma unroll
-                            for (int g2 = 0; g2 < kGroups; g2++) if ((unsigned)g2 == g) cq[g2]++;
-                            qk++;
-                            progress = true;
-                        }
-                    }
-                    if (pv < qk) {
-                        const unsigned itp = it + (unsigned)pv, vst = itp % (unsigned)a.stages, g = itp % kGroups;
-                        unsigned cpg = 0;
-#pragma unroll
-                        for (int g2 = 0; g2 < kGroups; g2++) if ((unsigned)g2 == g) cpg = cp[g2];
-                        if (mbar_test(bar_base + BAR_PFULL + 8 * g, cpg & 1u) && mbar_test(bar_base + BAR_OFREE + 8 * g, (cpg & 1u) ^ 1u)) {
-                            fence_after();
-                            const unsigned long long dv = make_desc(vring + vst * (unsigned)kVStride);
-                            const unsigned long long dp = make_desc(s_base + kOffPt + 2048u * g);
-#pragma unroll
-                            for (int k = 0; k < 4; k++) umma_i8(tmem + kColO + 16u * g, dv + 2u * k, dp + 2u * k, k > 0 ? 1u : 0u);
-                            umma_commit(bar_base + BAR_OFULL + 8 * g);
-                            umma_commit(bar_base + BAR_VEMPTY + 8 * vst);   /* V^T and the scales are consumed: the producer may refill the stage */
-                            if (itp < 8) TRACE(56 + itp);
-#pragma unroll
-                            for (int g2 = 0; g2 < kGroups; g2++) if ((unsigned)g2 == g) cp[g2]++;
-                            pv++;
-                            progress = true;
-                        }
-                    }
-                    if (progress) { idle_polls = 0; continue; }
-                    /* bounded: about 2^23 empty polls, far beyond any legitimate wait */
-                    if (++idle_polls > (1u << 23) || mi.abort_flag) {
-                        mi.abort_flag = 1;
-                        if (atomicCAS(a.err, 0u, 1u) == 0u) a.err[1] = 6u;
-                        ok = false;
-                    }
-                    __nanosleep(20);
+                if (ok && j0 < npg) ok = issue_qk(j0, 2u * (unsigned)group + (cnt & 1u));
+                if (ok && j0 + kGroups < npg) ok = issue_qk(j0 + kGroups, 2u * (unsigned)group + ((cnt + 1u) & 1u));
+                for (int j = j0; j < npg && ok; j += kGroups) {
+                    const unsigned itj = it + (unsigned)j, vst = itj % (unsigned)a.stages;
+                    ok = mbar_wait_blocking(bar_base + BAR_PFULL + 8 * group, cnt & 1u, &mi.abort_flag, a.err, 9u);
+                    if (!ok) break;
+                    fence_after();
+                    const unsigned long long dv = dv0 + (unsigned long long)(vst * (unsigned)(kVStride >> 4));
+                    const unsigned d = tmem + kColO + 16u * (unsigned)group;
+                    umma_i8(d, dv, dp, 0u); umma_i8(d, dv + 2u, dp + 2u, 1u); umma_i8(d, dv + 4u, dp + 4u, 1u); umma_i8(d, dv + 6u, dp + 6u, 1u);
+                    umma_commit(bar_base + BAR_OFULL + 8 * group);
+                    umma_commit(bar_base + BAR_VEMPTY + 8 * vst);   /* V^T and the scales are consumed: the producer may refill the stage */
+                    if (itj < 8) TRACE(56 + itj);
+                    if (j + 2 * kGroups < npg) ok = issue_qk(j + 2 * kGroups, 2u * (unsigned)group + (cnt & 1u));   /* the S^T buffer just read */
+                    cnt++;
                 }
                 it += (unsigned)npg;
+                if (newest_here) appends++;
                 u = sg.seg_u0 + sg.p_end;
             }
         }
@@ -436,7 +437,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
         signed char *s_qt = reinterpret_cast<signed char *>(s_dyn + kOffQt);
         uint8_t *s_pt = s_dyn + kOffPt + 2048 * group;
         const bool qwarp = warp < 8;   /* warps 0-7 also prepare the queries (warp = head) and run the segment's tail */
-        unsigned it = 0, cnt = 0;   /* ring position of the CTA; pages this group has processed */
+        unsigned it = 0, cnt = 0, segs_done = 0;   /* ring position of the CTA; pages this group has processed; segments started */
         long long u = u_begin;
         while (u < u_end) {
             const segment sg = locate(s_prefix, batch, n, G, u, u_end);
@@ -477,8 +478,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 if (lane == 0) mi.qf[warp] = sqv * (1.f / 254.f) * 0.08838834764831845f * kLog2e;
                 fence_async_smem();
             }
-            mbar_arrive(bar_base + BAR_QREADY);
             sm_sync();
+            if (tid == 0) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&mi.q_ready)), "r"(segs_done + 1u) : "memory");
+            segs_done++;
             float qf[kHpt];
 #pragma unroll
             for (int h = 0; h < kHpt; h++) qf[h] = mi.qf[kHpt * half + h];
@@ -491,7 +493,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
             bool pending_o = false;
             const int npg = sg.p_end - sg.p_begin;
             const unsigned c_hi = (unsigned)(kHpt * half), c_lo = 8u + (unsigned)(kHpt * half);   /* this half's columns: high / low digits */
-            for (int j = (int)(((unsigned)group - it) % kGroups); j < npg; j += kGroups) {
+            const int j0 = (int)(((unsigned)group - it) % kGroups);
+            for (int j = j0; j < npg; j += kGroups) {
                 const unsigned itj = it + (unsigned)j, vst = itj % (unsigned)a.stages, vph = (itj / (unsigned)a.stages) & 1u;
                 const int p = sg.p_begin + j;
                 const uint8_t *sp = s_dyn + vring_off + (size_t)vst * kVStride;
@@ -503,7 +506,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 int rh[kHpt], rl[kHpt];
                 tmem_ld_pair(tmem + t_lane + 16u * sb + c_hi, tmem + t_lane + 16u * sb + c_lo, rh, rl);
                 fence_before();
-                mbar_arrive(bar_base + BAR_SFREE + 8 * sb);
                 if (warp == 0 && cnt == 1) TRACE(18);
                 if (pending_o) {
                     /* O^T of this group's previous page (its digits are relative to the current m_ref) */
@@ -512,7 +514,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                     int oh[kHpt], ol[kHpt];
                     tmem_ld_pair(tmem + t_lane + kColO + 16u * (unsigned)group + c_hi, tmem + t_lane + kColO + 16u * (unsigned)group + c_lo, oh, ol);
                     fence_before();
-                    mbar_arrive(bar_base + BAR_OFREE + 8 * group);
 #pragma unroll
                     for (int h = 0; h < kHpt; h++) acc[h] += (float)(oh[h] * 254 + ol[h]) * ostep;
                 }
@@ -559,7 +560,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 }
                 if (warp == 0 && cnt == 1) TRACE(22);
                 fence_async_smem();
-                mbar_arrive(bar_base + BAR_PFULL + 8 * group);
+                mbar_arrive(bar_base + BAR_PFULL + 8 * group);   /* digits written, S^T and O^T read: over to the group's issuer */
                 pending_o = true;
                 cnt++;
                 if (warp == 0) TRACE(3 + j / kGroups);
@@ -570,7 +571,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 int oh[kHpt], ol[kHpt];
                 tmem_ld_pair(tmem + t_lane + kColO + 16u * (unsigned)group + c_hi, tmem + t_lane + kColO + 16u * (unsigned)group + c_lo, oh, ol);
                 fence_before();
-                mbar_arrive(bar_base + BAR_OFREE + 8 * group);
 #pragma unroll
                 for (int h = 0; h < kHpt; h++) acc[h] += (float)(oh[h] * 254 + ol[h]) * ostep;
             }
@@ -721,7 +721,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
     /* ---- everyone meets here; TMEM goes back */
     fence_before();
     __syncthreads();
-    if (warp == kSmWarps + 1 && !idle) {
+    if (warp == kSmWarps && !idle) {
         fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
     }

@@ -107,6 +107,37 @@ def test_decode_ragged_batch_and_poison(cuda, oracle, monkeypatch, tc):
     ctx.close()
 
 
+@pytest.mark.parametrize("tc", [False, True])
+def test_decode_many_segments_share_ctas(cuda, oracle, monkeypatch, tc):
+    """More (row, KV head) segments than CTAs: every CTA walks through several segments and segments straddle CTAs
+    (the equal-unit-range schedule); a fused step, so that the appends land in many different CTAs."""
+    import torch
+    from hy3_b200 import Hy3Attn
+    monkeypatch.setenv("HY3A_INT8_TC", "1" if tc else "0")
+    rng = np.random.default_rng(7)
+    lens0 = [int(x) for x in rng.integers(1, 900, size=40)]      # 320 segments for 148 CTAs
+    lens0[3], lens0[17] = 0, 2600
+    B = len(lens0)
+    ctx = Hy3Attn(kv_dtype="int8", n_layers=1, max_seqs=B, max_batch=B, max_tokens=sum(lens0) + 256 * B, max_tokens_per_seq=4096)
+    for s_, n0 in enumerate(lens0):
+        if n0:
+            ctx.fill_random(0, s_, 0, n0, 500 + s_)
+    q = oracle.fill_normal((2, B, 64, 128), SEED, 331)
+    k = oracle.fill_normal((2, B, 8, 128), SEED, 332)
+    v = oracle.fill_normal((2, B, 8, 128), SEED, 333)
+    tq, tk, tv = (torch.from_numpy(x).to(cuda) for x in (q, k, v))
+    qo = torch.zeros((B, 64, 128), dtype=torch.float32, device=cuda)
+    for t in range(2):
+        ctx.batch_set(list(range(B)), [n0 + t for n0 in lens0])
+        out = ctx.decode_step(0, tq[t], tk[t], tv[t], q_out=qo)
+    ctx.sync()
+    out, qo = out.cpu().numpy(), qo.cpu().numpy()
+    for s_ in range(B):
+        ks, vs = ctx.export_kv(0, s_, 0, lens0[s_] + 2)
+        check_attention(out[s_], oracle.attention(qo[s_], slots_to_float(oracle, ks, "int8"), slots_to_float(oracle, vs, "int8")), "seq %d len %d" % (s_, lens0[s_] + 2))
+    ctx.close()
+
+
 def test_append_then_decode_end_to_end(cuda, oracle):
     """The real step: fused append of token t, then attention over [0, t], for a few steps."""
     import torch
