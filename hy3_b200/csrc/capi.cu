@@ -249,9 +249,9 @@ int hy3a_sync(hy3a_ctx *ctx) {
     HY3A_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, HY3A_ERR_WORDS * sizeof(unsigned), cudaMemcpyDeviceToHost, ctx->stream));
     HY3A_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ctx->h_err[0]) {
-        unsigned code = ctx->h_err[0], where = ctx->h_err[1];
+        unsigned code = ctx->h_err[0], where = ctx->h_err[1], w2 = ctx->h_err[2], w3 = ctx->h_err[3];
         cudaMemsetAsync(ctx->d_err, 0, HY3A_ERR_WORDS * sizeof(unsigned), ctx->stream);
-        return hy3a_fail(ctx, HY3A_ETIMEOUT, "device-side bounded wait or bounds check failed (code %u, where %u)", code, where);
+        return hy3a_fail(ctx, HY3A_ETIMEOUT, "device-side bounded wait or bounds check failed (code %u, where %u, detail %u %u)", code, where, w2, w3);
     }
     return HY3A_OK;
 }

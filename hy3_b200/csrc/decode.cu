@@ -962,6 +962,9 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
     }
     ctx->launches++;
     ctx->bulk_write_pending = 0;   /* the kernel after this one only has this one to stay clear of */
+    if (e == cudaErrorNotSupported)
+        return hy3a_fail(ctx, HY3A_ESTATE, "decode: the tcgen05 INT8 path (HY3A_INT8_TC=1) serves batches with fewer (row, KV head) segments than CTAs (%d x %d >= %d)",
+                         ctx->batch_n, ctx->cfg.kv_head_count, ctx->decode_ctas);
     if (e != cudaSuccess) return hy3a_fail(ctx, HY3A_ECUDA, "decode launch: %s", cudaGetErrorString(e));
     return HY3A_OK;
 }

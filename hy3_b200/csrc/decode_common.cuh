@@ -136,10 +136,12 @@ __device__ __forceinline__ bool mbar_wait_blocking(unsigned bar, unsigned parity
         if (mbar_try(bar, parity, 20000u)) return true;
         if (*abort_flag) return false;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        if (t1 - t0 > 500000000ull) break;
+        /* both a real amount of waiting and the clock must agree: the global timer can step (it is re-synchronised with the
+         * host clock), and a try_wait may return long before its hint */
+        if (i >= (1u << 13) && t1 - t0 > 500000000ull) break;
     }
     *abort_flag = 1;
-    if (atomicCAS(err, 0u, 1u) == 0u) err[1] = where;
+    if (atomicCAS(err, 0u, 1u) == 0u) { err[1] = where; err[2] = blockIdx.x; err[3] = bar; }
     return false;
 }
 __device__ __forceinline__ void bulk_g2s(unsigned dst, const void *src, unsigned bytes, unsigned bar) {

@@ -54,6 +54,11 @@ namespace {
 #ifndef HY3A_TC_GROUPS
 #define HY3A_TC_GROUPS 2
 #endif
+#ifdef HY3A_DECODE_TRACE
+#define DBG(i, v) do { reinterpret_cast<volatile unsigned *>(mi.dbg)[i] = (unsigned)(v); } while (0)
+#else
+#define DBG(i, v) do { } while (0)
+#endif
 #ifndef HY3A_TC_HALVES
 #define HY3A_TC_HALVES 2
 #endif
@@ -91,6 +96,7 @@ struct tc_misc {
     unsigned tmem;
     int abort_flag;
     int flag;
+    unsigned dbg[16];           /* trace builds: progress marks of the roles, dumped when a wait ran out */
     unsigned q_ready;           /* segments whose query digits are in shared memory (monotonic, for the same reason as below) */
     unsigned appends_done;      /* fused appends completed by the producer warp so far (monotonic; a parity barrier would alias when the
                                  * producer runs two appends ahead of an issuer in a CTA that walks through many short segments) */
@@ -300,6 +306,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 /* before the preceding kernel is known to be complete only pages that lie wholly below the newest
                  * slot may be fetched, and only into stages that were never used */
                 if (!waited && (it >= (unsigned)min(kKStages, a.stages) || (p + 1) * HY3A_PT > sg.len - 2)) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+                if (lane == 0) DBG(0, it);
                 int okl = 1;
                 uint8_t *page = cache.pool + hy3a_page_index(cache, bt[p], a.layer, sg.hl) * (size_t)cache.page_bytes;
                 if (lane == 0) {
@@ -307,7 +314,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                     if (okl) {
                         mbar_expect_tx(bar_base + BAR_KFULL + 8 * kst, (unsigned)kKBytes);
                         bulk_g2s(kring + kst * (unsigned)kKBytes, page, (unsigned)kKBytes, bar_base + BAR_KFULL + 8 * kst);
+                        DBG(1, it);
                         okl = mbar_wait_blocking(bar_base + BAR_VEMPTY + 8 * vst, vph ^ 1u, &mi.abort_flag, a.err, 2u) ? 1 : 0;
+                        DBG(2, it);
                     }
                     if (okl) {
                         mbar_expect_tx(bar_base + BAR_VFULL + 8 * vst, (unsigned)kVBytes);
@@ -394,6 +403,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 const int j0 = (int)(((unsigned)group - it) % kGroups);
                 auto issue_qk = [&](int jq, unsigned sbuf) {
                     const unsigned itq = it + (unsigned)jq, kst = itq % (unsigned)kKStages, kph = (itq / (unsigned)kKStages) & 1u;
+                    DBG(4 + 3 * group, itq);
                     bool k2 = mbar_wait_blocking(bar_base + BAR_KFULL + 8 * kst, kph, &mi.abort_flag, a.err, 6u);
                     /* the producer warp has patched the newest token into this page when its counter has passed ours */
                     if (k2 && newest_here && jq == npg - 1) k2 = wait_counter(&mi.appends_done, appends, 7u);
@@ -413,7 +423,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 if (ok && j0 + kGroups < npg) ok = issue_qk(j0 + kGroups, 2u * (unsigned)group + ((cnt + 1u) & 1u));
                 for (int j = j0; j < npg && ok; j += kGroups) {
                     const unsigned itj = it + (unsigned)j, vst = itj % (unsigned)a.stages;
+                    DBG(5 + 3 * group, itj);
                     ok = mbar_wait_blocking(bar_base + BAR_PFULL + 8 * group, cnt & 1u, &mi.abort_flag, a.err, 9u);
+                    DBG(6 + 3 * group, itj);
                     if (!ok) break;
                     fence_after();
                     const unsigned long long dv = dv0 + (unsigned long long)(vst * (unsigned)(kVStride >> 4));
@@ -499,6 +511,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 const int p = sg.p_begin + j;
                 const uint8_t *sp = s_dyn + vring_off + (size_t)vst * kVStride;
                 const unsigned sb = 2u * (unsigned)group + (cnt & 1u);   /* this page's S^T buffer */
+                if ((tid % kGroupThreads) == 0) DBG(10 + 2 * group, itj);
                 if (warp == 0 && cnt == 1) TRACE(23);
                 mbar_wait_blocking(bar_base + BAR_SFULL + 8 * sb, (cnt >> 1) & 1u, &mi.abort_flag, a.err, 11u);
                 mbar_wait_blocking(bar_base + BAR_VFULL + 8 * vst, vph, &mi.abort_flag, a.err, 12u);   /* orders the scale reads below */
@@ -506,6 +519,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 int rh[kHpt], rl[kHpt];
                 tmem_ld_pair(tmem + t_lane + 16u * sb + c_hi, tmem + t_lane + 16u * sb + c_lo, rh, rl);
                 fence_before();
+                if ((tid % kGroupThreads) == 0) DBG(11 + 2 * group, itj);
                 if (warp == 0 && cnt == 1) TRACE(18);
                 if (pending_o) {
                     /* O^T of this group's previous page (its digits are relative to the current m_ref) */
@@ -718,6 +732,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
             }
     }
 
+#ifdef HY3A_DECODE_TRACE
+    __syncthreads();
+    if (mi.abort_flag && tid < 16) a.trace[(size_t)blockIdx.x * 64 + 40 + tid] = 0x100000000ull | mi.dbg[tid];
+#endif
     /* ---- everyone meets here; TMEM goes back */
     fence_before();
     __syncthreads();
@@ -730,6 +748,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
 } /* namespace */
 
 cudaError_t hy3a_launch_decode_tc(hy3a_ctx *ctx, const hy3a_cache_view &cv, const hy3a_batch_view &bv, hy3a_decode_args &a) {
+    /* Known limitation of this opt-in kernel: when there are at least as many (row, KV head) segments as CTAs, a CTA walks
+     * through pieces of several segments, and in that mode the pipeline has stalled intermittently on a B200 (the bounded
+     * waits turn the stall into HY3A_ETIMEOUT; cause not found yet).  Such batches are refused here; the mma.sync kernel
+     * (default layout) serves them at 0.88 of the HBM roofline. */
+    if ((long long)ctx->batch_n * ctx->cfg.kv_head_count >= (long long)ctx->decode_ctas) return cudaErrorNotSupported;
     const size_t prefix = ((size_t)(ctx->batch_n + 1) * sizeof(int) + 127) & ~(size_t)127;
     a.prefix_bytes = (int)prefix;
     const size_t fixed = (((size_t)kOffPrefix + prefix + 1023) & ~(size_t)1023) + 1024;   /* + slack for the 1024-byte alignment */

@@ -526,13 +526,22 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tmem_ld32(tm_s + lane_base + 64u * hf, v0);
             tmem_ld32(tm_s + lane_base + 64u * hf + 32u, v1);
             float mx = -INFINITY;
+            if (masked) {      /* only the tiles on the diagonal pay for the causal test */
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                float s0 = __uint_as_float(v0[i]) * kScaleLog2, s1 = __uint_as_float(v1[i]) * kScaleLog2;
-                if (masked && k0 + i > qpos) s0 = -INFINITY;
-                if (masked && k0 + 32 + i > qpos) s1 = -INFINITY;
-                v0[i] = __float_as_uint(s0); v1[i] = __float_as_uint(s1);
-                mx = fmaxf(mx, fmaxf(s0, s1));
+                for (int i = 0; i < 32; i++) {
+                    float s0 = __uint_as_float(v0[i]) * kScaleLog2, s1 = __uint_as_float(v1[i]) * kScaleLog2;
+                    if (k0 + i > qpos) s0 = -INFINITY;
+                    if (k0 + 32 + i > qpos) s1 = -INFINITY;
+                    v0[i] = __float_as_uint(s0); v1[i] = __float_as_uint(s1);
+                    mx = fmaxf(mx, fmaxf(s0, s1));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const float s0 = __uint_as_float(v0[i]) * kScaleLog2, s1 = __uint_as_float(v1[i]) * kScaleLog2;
+                    v0[i] = __float_as_uint(s0); v1[i] = __float_as_uint(s1);
+                    mx = fmaxf(mx, fmaxf(s0, s1));
+                }
             }
             xch[hf * 128 + r] = mx;
             asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
@@ -543,11 +552,12 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             float lsum = 0.f;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                const unsigned p0 = pack_h2(ex2f(__uint_as_float(v0[i]) - m_new), ex2f(__uint_as_float(v0[i + 1]) - m_new));
-                const unsigned p1 = pack_h2(ex2f(__uint_as_float(v1[i]) - m_new), ex2f(__uint_as_float(v1[i + 1]) - m_new));
-                pk[i >> 1] = p0; pk[16 + (i >> 1)] = p1;
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&p0)), f1 = __half22float2(*reinterpret_cast<const __half2 *>(&p1));
-                lsum += (f0.x + f0.y) + (f1.x + f1.y);
+                /* the denominator sums the unrounded values: the fp16 rounding of P is a zero-mean 2^-12 relative error per
+                 * term, far below the tolerance */
+                const float e0 = ex2f(__uint_as_float(v0[i]) - m_new), e1 = ex2f(__uint_as_float(v0[i + 1]) - m_new);
+                const float e2 = ex2f(__uint_as_float(v1[i]) - m_new), e3 = ex2f(__uint_as_float(v1[i + 1]) - m_new);
+                pk[i >> 1] = pack_h2(e0, e1); pk[16 + (i >> 1)] = pack_h2(e2, e3);
+                lsum += (e0 + e1) + (e2 + e3);
             }
             /* O_x is only ours again when P_x(j-1).V_(j-1) has completed */
             if (j > 0 && ok) {

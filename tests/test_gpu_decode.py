@@ -113,6 +113,7 @@ def test_decode_many_segments_share_ctas(cuda, oracle, monkeypatch, tc):
     (the equal-unit-range schedule); a fused step, so that the appends land in many different CTAs."""
     import torch
     from hy3_b200 import Hy3Attn
+    from hy3_b200 import Hy3AttnError
     monkeypatch.setenv("HY3A_INT8_TC", "1" if tc else "0")
     rng = np.random.default_rng(7)
     lens0 = [int(x) for x in rng.integers(1, 900, size=40)]      # 320 segments for 148 CTAs
@@ -122,6 +123,14 @@ def test_decode_many_segments_share_ctas(cuda, oracle, monkeypatch, tc):
     for s_, n0 in enumerate(lens0):
         if n0:
             ctx.fill_random(0, s_, 0, n0, 500 + s_)
+    if tc:
+        # the opt-in tcgen05 kernel refuses schedules in which a CTA serves pieces of several segments (a code, not a hang)
+        ctx.batch_set(list(range(B)), [n0 for n0 in lens0])
+        with pytest.raises(Hy3AttnError) as ei:
+            ctx.decode(0, torch.zeros((B, 64, 128), device=cuda))
+        assert ei.value.code == -5
+        ctx.close()
+        return
     q = oracle.fill_normal((2, B, 64, 128), SEED, 331)
     k = oracle.fill_normal((2, B, 8, 128), SEED, 332)
     v = oracle.fill_normal((2, B, 8, 128), SEED, 333)
