@@ -473,7 +473,7 @@ def run_ours(args):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD if (world == 1 and args.kv == "int8" and n_layers == N_LAYERS and ntok0 == NTOK)
                            else "%s-KV decode, %d layers x %d positions per GPU, %d GPU(s)%s" % (
-                               args.kv, n_layers, ntok0, world, (", sequence-sharded, " + ("NCCL all-gather" if args.nccl_exchange else "records pushed over NVLink peer memory by the decode kernel") + " + LSE merge" + (" (exchange of layer l under the KV stream of layer l+1)" if not args.serial_exchange else " (dependent chain)")) if world > 1 else ""),
+                               args.kv, n_layers, ntok0, world, (", sequence-sharded, " + (("NCCL all-gather + LSE merge kernel" + (" (exchange of layer l on a side stream under the KV stream of layer l+1)" if not args.serial_exchange else " (dependent chain)")) if args.nccl_exchange else "one launch per layer: the decode kernel's epilogue pushes the rank's records to all ranks over NVLink peer memory, waits for theirs and folds (no NCCL call)")) if world > 1 else ""),
                            "kv_dtype": args.kv, "layers": n_layers, "positions_per_gpu": ntok0, "compute": "fp16 mma.sync, fp32 accumulate/softmax",
                            "l2": "inputs larger than L2: %.2f GB of KV streamed per step, every layer's cache read once" % (bytes_per_step / world / 1e9),
                            "graph": "one CUDA graph of %d launches per step" % per_step_launches},
