@@ -821,7 +821,14 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 fa.out = a.out + (size_t)row * a.out_stride + ((size_t)(cache.kv_head_begin + hl) * 8 + h) * HY3A_D + d4;
                 fa.n_ranks = a.n_dest; fa.my_rank = a.my_rank; fa.line_a = 1 + (d4 >> 1); fa.flag = flag; fa.stage = reinterpret_cast<const uint4 *>(s_dyn); fa.h = h; fa.lane = lane;
                 fa.own_m = m_nat; fa.own_l = L; fa.own_acc[0] = acc[0]; fa.own_acc[1] = acc[1]; fa.own_acc[2] = acc[2]; fa.own_acc[3] = acc[3];
-                shard_fold<kShardBatch>(fa);
+                if (STAGED && aligned && (size_t)a.stages * geom.page_bytes >= (size_t)8 * 8 * kShardLines * 16) {
+                    /* CTA-aligned segments: the page ring is idle by now and holds all 8 ranks' records at once, so
+                     * every rank is polled in the same round */
+                    fa.stage = reinterpret_cast<const uint4 *>(s_dyn + kFixed + a.prefix_bytes + 128);
+                    shard_fold<8>(fa);
+                } else {
+                    shard_fold<kShardBatch>(fa);
+                }
                 if (warp == 0) TRACE(30);
             }
             consumer_sync();                 /* every thread has read the use count */

@@ -695,7 +695,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) hy3a_decode_tc_kernel(hy3a_cach
                 fa.n_ranks = a.n_dest; fa.my_rank = a.my_rank; fa.line_a = 1 + (d4 >> 1); fa.flag = flag;
                 fa.stage = reinterpret_cast<const uint4 *>(s_dyn + kOffLand); fa.h = h; fa.lane = lane;
                 fa.own_m = m_nat; fa.own_l = L; fa.own_acc[0] = accv[0]; fa.own_acc[1] = accv[1]; fa.own_acc[2] = accv[2]; fa.own_acc[3] = accv[3];
-                if (red) shard_fold<kLandPieces>(fa);
+                if (red) {
+                    if (aligned && (size_t)a.stages * kVStride >= (size_t)8 * 8 * kShardLines * 16) {
+                        fa.stage = reinterpret_cast<const uint4 *>(s_dyn + vring_off);   /* the idle V ring holds all 8 ranks' records */
+                        shard_fold<8>(fa);
+                    } else {
+                        shard_fold<kLandPieces>(fa);
+                    }
+                }
                 if (warp == 0) TRACE(30);
                 sm_sync();                 /* every thread has read the use count */
                 if (tid == 0) a.shard_round[seg] += 1u;

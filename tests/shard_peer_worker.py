@@ -73,7 +73,9 @@ def main():
                 want = full.decode_step(l, tq[t, l], tk[t, l], tv[t, l], q_out=qo)
                 full.sync()
                 worst = max(worst, float((want - outs[t, l]).abs().max()))
-        assert worst <= 1e-4, "sharded vs single-GPU: %g" % worst
+        # not bit-equal: the ranks cut the sequence elsewhere than the CTAs of one GPU do; fp16 P (mma.sync kernel) differs by
+        # ~1e-5, the two-digit fixed-point P of the tcgen05 kernel by ~1e-4 -- both far inside the 2e-3 bound checked below
+        assert worst <= 5e-4, "sharded vs single-GPU: %g" % worst
         for s_ in range(B):                   # last step, last layer, against the oracle on the stored cache
             ks, vs = full.export_kv(L - 1, s_, 0, lens0[s_] + steps)
             check_attention(outs[-1, -1, s_].cpu().numpy(),
