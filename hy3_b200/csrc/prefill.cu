@@ -102,6 +102,13 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+/* the same load without the wait: several loads can be in flight before one tcgen05.wait::ld */
+__device__ __forceinline__ void tmem_ld32_nowait(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
@@ -523,8 +530,9 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             const int k0 = j * kKeys + 64 * hf;                    /* first key of this thread's columns */
             const bool masked = (j * kKeys + kKeys - 1 > a.base + tq0);   /* the tile crosses the diagonal of some row */
             unsigned v0[32], v1[32];
-            tmem_ld32(tm_s + lane_base + 64u * hf, v0);
-            tmem_ld32(tm_s + lane_base + 64u * hf + 32u, v1);
+            tmem_ld32_nowait(tm_s + lane_base + 64u * hf, v0);
+            tmem_ld32_nowait(tm_s + lane_base + 64u * hf + 32u, v1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             float mx = -INFINITY;
             if (masked) {      /* only the tiles on the diagonal pay for the causal test */
 #pragma unroll
