@@ -472,12 +472,19 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
          * S_x(j+1) overwrites the columns P_x(j) lives in, so it is issued behind PV_x(j) (the tensor core runs in order) */
         if (lane == 0) {
             bool ok = mbar_wait(BAR(B2_Q), 0u, s_abort, a.err, 20u);
+            /* descriptors are computed once; inside the loops a k-step is one 64-bit add (the offsets stay inside the
+             * 14-bit address field: all tiles lie in the first 256 KB of shared memory) -- the scalar code between two
+             * tcgen05.mma of this lane is what bounds the issue rate */
+            const unsigned long long dQ[2] = {make_desc(sbase + kOff2Q), make_desc(sbase + kOff2Q + kTileBytes)};
+            const unsigned long long dK[2] = {make_desc(sbase + kOff2K), make_desc(sbase + kOff2K + kTileBytes)};
+            const unsigned long long dV[2] = {make_desc(sbase + kOff2V), make_desc(sbase + kOff2V + kTileBytes)};
             auto issue_qk = [&](int x, int j) {      /* S_x(j) = Q_x . K_j^T : 8 k-steps of 16 over d = 128 */
-                const int st = j & 1;
+                const unsigned long long q = dQ[x], k = dK[j & 1];
+                const unsigned d = tmem + 128u * x;
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) {
-                    const unsigned off = (unsigned)(kk >> 2) * 16384u + (unsigned)(kk & 3) * 32u;
-                    umma_f16(tmem + 128u * x, make_desc(sbase + kOff2Q + x * kTileBytes + off), make_desc(sbase + kOff2K + st * kTileBytes + off), kk > 0);
+                    const unsigned long long off = (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2);   /* (16 384 B | 32 B) >> 4 */
+                    umma_f16(d, q + off, k + off, kk > 0);
                 }
                 umma_commit(BAR(B2_SF + x));
             };
@@ -498,10 +505,15 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     /* O_x += P_x(j) . V_j : 8 k-steps of 16 keys; A = 8 columns of packed fp16 pairs per step */
+                    {
+                        const unsigned long long v = dV[st];
+                        const unsigned d = tmem + 256u + 128u * x, pa = tmem + 128u * x;
+                        const unsigned acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
-                    for (int kk = 0; kk < 8; kk++) {
-                        const unsigned off = (unsigned)(kk >> 2) * 16384u + (unsigned)(kk & 3) * 32u;
-                        umma_f16_ta(tmem + 256u + 128u * x, tmem + 128u * x + 8u * kk, make_desc(sbase + kOff2V + st * kTileBytes + off), (j > 0 || kk > 0));
+                        for (int kk = 0; kk < 8; kk++) {
+                            const unsigned long long off = (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2);
+                            umma_f16_ta(d, pa + 8u * kk, v + off, kk > 0 ? 1u : acc0);
+                        }
                     }
                     umma_commit(BAR(B2_O + x));
                     if (x == 1) umma_commit(BAR(B2_VE + st));
