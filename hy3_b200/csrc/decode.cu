@@ -892,7 +892,8 @@ template <int DT>
 static cudaError_t launch_decode_dt(hy3a_ctx *ctx, const hy3a_cache_view &cv, const hy3a_batch_view &bv, decode_args &a) {
     const size_t prefix = ((size_t)(ctx->batch_n + 1) * sizeof(int) + 127) & ~(size_t)127;
     dim3 grid(ctx->decode_ctas);
-    static bool attr_set[3][3] = {{false, false, false}, {false, false, false}, {false, false, false}};
+    static bool attr_dev[64][3][3];   /* function attributes are per device: [device ordinal][cache type][variant] */
+    bool (*attr_set)[3] = attr_dev[ctx->device & 63];
     a.prefix_bytes = (int)prefix;
     if (ctx->decode_stages >= 2) {
         a.stages = ctx->decode_stages;

@@ -769,7 +769,8 @@ cudaError_t hy3a_launch_decode_tc(hy3a_ctx *ctx, const hy3a_cache_view &cv, cons
     if (stages < 2) return cudaErrorInvalidConfiguration;
     a.stages = stages;
     const size_t smem = fixed + (size_t)kKStages * kKBytes + (size_t)stages * kVStride;
-    static bool attr_set[2] = {false, false};
+    static bool attr_dev[64][2];   /* function attributes are per device */
+    bool *attr_set = attr_dev[ctx->device & 63];
     const bool shard = a.n_dest > 0;
     if (!attr_set[shard ? 1 : 0]) {
         cudaError_t e = shard ? cudaFuncSetAttribute(hy3a_decode_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax)

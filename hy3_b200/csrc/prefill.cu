@@ -715,7 +715,8 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
         rc = make_map(ctx, &tv, ctx->d_pf_v, dv, sv, bv);
         if (rc) return rc;
     }
-    static bool attr_set = false;
+    static bool attr_dev[64];   /* function attributes are per device */
+    bool &attr_set = attr_dev[ctx->device & 63];
     if (!attr_set) {
         HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel_v1, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
         HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPf2Smem));
