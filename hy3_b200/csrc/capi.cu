@@ -109,6 +109,7 @@ void hy3a_destroy(hy3a_ctx *ctx) {
     cudaFree(ctx->pool); cudaFree(ctx->d_block_table); cudaFree(ctx->d_vs_max); cudaFree(ctx->d_inv_freq);
     cudaFree(ctx->d_norm_w); cudaFree(ctx->d_batch); cudaFree(ctx->d_partials); cudaFree(ctx->d_counters); cudaFree(ctx->d_err);
     cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v); cudaFree(ctx->d_trace);
+    for (int l = 0; l < HY3A_MAX_LAYERS; l++) { cudaFree(ctx->pf_mk[l]); cudaFree(ctx->pf_mv[l]); }
     hy3a_shard_disconnect(ctx);
     cudaFree(ctx->shard_local);
     if (ctx->h_ring) cudaFreeHost(ctx->h_ring);
@@ -166,6 +167,9 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     if (ctx->decode_ctas > hy3a_decode_max_ctas()) ctx->decode_ctas = hy3a_decode_max_ctas();
     if (ctx->decode_ctas > 512) ctx->decode_ctas = 512;
     { const char *e = getenv("HY3A_NO_PDL"); ctx->use_pdl = !(e && atoi(e)); }
+    /* fp16 operand mirrors of the chunked prefill: at most this much device memory beside the pool */
+    { const char *e = getenv("HY3A_PF_MIRROR_MB"); ctx->pf_mbudget = (size_t)(e ? (atoll(e) > 0 ? atoll(e) : 0) : 8192) << 20; }
+    ctx->pf_mseq = -1;
     {   /* ring depth: as many pages as fit in shared memory beside the merge buffers, at most 8 */
         ctx->decode_stages = hy3a_decode_ring_capacity(ctx->geom.page_bytes, cfg->max_batch);
         const char *e = getenv("HY3A_DECODE_STAGES");
@@ -321,6 +325,7 @@ int hy3a_seq_release(hy3a_ctx *ctx, int seq, int keep_ntok) {
     if (seq < 0 || seq >= ctx->cfg.max_seqs) return hy3a_fail(ctx, HY3A_EINVAL, "seq %d out of range", seq);
     if (keep_ntok < 0) keep_ntok = 0;
     int keep = (keep_ntok + HY3A_PAGE_TOKENS - 1) / HY3A_PAGE_TOKENS;
+    hy3a_mirror_truncate(ctx, seq, -1, keep_ntok);
     int *row = ctx->h_block_table + (size_t)seq * ctx->cfg.max_blocks_per_seq;
     while (ctx->h_seq_blocks[seq] > keep) {
         int b = --ctx->h_seq_blocks[seq];
@@ -344,6 +349,7 @@ int hy3a_batch_set(hy3a_ctx *ctx, int n, const int *seq_ids, const int *slots, c
         if (slots[i] < -1) return hy3a_fail(ctx, HY3A_EINVAL, "batch_set: row %d slot %d < -1", i, slots[i]);
         int rc = hy3a_seq_reserve(ctx, seq_ids[i], slots[i] + 1);
         if (rc) return rc;
+        if (slots[i] >= 0) hy3a_mirror_truncate(ctx, seq_ids[i], -1, slots[i]);   /* the slot is about to be written */
     }
     /* one staging copy of [seq | slot | pos], each padded to max_batch */
     size_t mb = (size_t)ctx->cfg.max_batch;
@@ -514,7 +520,7 @@ static int xport(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint8_t *k_sl
     if (!ctx) return HY3A_EINVAL;
     if (layer < 0 || layer >= ctx->cfg.n_layers || seq < 0 || seq >= ctx->cfg.max_seqs || t0 < 0 || n < 1 || !k_slots || !v_slots)
         return hy3a_fail(ctx, HY3A_EINVAL, "%s: bad argument", import ? "import_kv" : "export_kv");
-    if (import) { int rc = hy3a_seq_reserve(ctx, seq, t0 + n); if (rc) return rc; }
+    if (import) { int rc = hy3a_seq_reserve(ctx, seq, t0 + n); if (rc) return rc; hy3a_mirror_truncate(ctx, seq, layer, t0); }
     else if (t0 + n > ctx->h_seq_blocks[seq] * HY3A_PAGE_TOKENS) return hy3a_fail(ctx, HY3A_EINVAL, "export_kv: tokens [%d,%d) not mapped", t0, t0 + n);
     size_t bytes = (size_t)n * hy3a_slot_bytes(ctx->cfg.kv_dtype);
     uint8_t *dk = NULL, *dv = NULL;
@@ -546,6 +552,7 @@ int hy3a_fill_random(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint64_t 
     if (layer < 0 || layer >= ctx->cfg.n_layers || seq < 0 || seq >= ctx->cfg.max_seqs || t0 < 0 || n < 1) return hy3a_fail(ctx, HY3A_EINVAL, "fill_random: bad argument");
     int rc = hy3a_seq_reserve(ctx, seq, t0 + n);
     if (rc) return rc;
+    hy3a_mirror_truncate(ctx, seq, layer, t0);
     return hy3a_launch_fill_random(ctx, layer, seq, t0, n, seed);
 }
 

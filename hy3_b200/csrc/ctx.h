@@ -65,6 +65,14 @@ struct hy3a_ctx {
     unsigned int *d_counters; /* decode scratch: [max_batch*kv_heads] arrival counters (self-resetting) */
     void *d_pf_k, *d_pf_v; /* prefill: fp16 staging of dequantised K / V pages (INT8/INT4 caches) */
     size_t pf_bytes;
+    /* prefill operand mirrors: per layer, the fp16 tensor-core image (K rows, V transposed) of ONE sequence's tokens
+     * [0, pf_mntok[layer]), kept across chunks so that a chunk only converts the pages it appended.  Any call that
+     * can write a slot below pf_mntok (batch_set rows, import, fill, release) lowers pf_mntok first. */
+    void *pf_mk[HY3A_MAX_LAYERS], *pf_mv[HY3A_MAX_LAYERS];
+    int pf_mcap[HY3A_MAX_LAYERS];   /* tokens of capacity (multiple of 1024) */
+    int pf_mntok[HY3A_MAX_LAYERS];  /* tokens converted and still valid */
+    int pf_mseq;                    /* the sequence all mirrors belong to, -1 = none */
+    size_t pf_mbytes, pf_mbudget;   /* allocated / allowed bytes of mirrors (HY3A_PF_MIRROR_MB, 0 = no mirrors) */
     unsigned long long *d_trace; /* [512][64] timestamps written by trace builds of the decode kernel */
     unsigned int *d_err;  /* HY3A_ERR_WORDS words: kernels record bounded-wait timeouts / bad indices here */
     size_t partial_records;
@@ -123,6 +131,14 @@ int hy3a_launch_init_pages(hy3a_ctx *ctx, size_t first_page, size_t n_pages);
 int hy3a_decode_ring_capacity(int page_bytes, int max_batch);
 int hy3a_decode_max_ctas(void);
 int hy3a_fail(hy3a_ctx *ctx, int code, const char *fmt, ...);
+
+/* slots >= ntok of sequence seq (all layers, or one layer if layer >= 0) are about to be rewritten or dropped */
+static inline void hy3a_mirror_truncate(hy3a_ctx *c, int seq, int layer, int ntok) {
+    if (seq != c->pf_mseq) return;
+    if (ntok < 0) ntok = 0;
+    if (layer >= 0) { if (c->pf_mntok[layer] > ntok) c->pf_mntok[layer] = ntok; return; }
+    for (int l = 0; l < c->cfg.n_layers; l++) if (c->pf_mntok[l] > ntok) c->pf_mntok[l] = ntok;
+}
 
 static inline hy3a_cache_view hy3a_view(const hy3a_ctx *c) {
     hy3a_cache_view v;

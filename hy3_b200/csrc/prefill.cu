@@ -72,6 +72,27 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     if (atomicCAS(err, 0u, 2u) == 0u) err[1] = where;
     return false;
 }
+/* the same bound with mbarrier.try_wait, which suspends the thread until the phase completes or the hint elapses: the
+ * waiter wakes within tens of ns of the arrival instead of at its next poll */
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity, unsigned hint_ns) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_blocking(unsigned bar, unsigned parity, volatile int *abort_flag, unsigned *err, unsigned where) {
+    if (mbar_try(bar, parity, 2000u)) return true;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (unsigned i = 0; i < (1u << 22); i++) {
+        if (mbar_try(bar, parity, 20000u)) return true;
+        if (*abort_flag) return false;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (i >= (1u << 13) && t1 - t0 > 500000000ull) break;   /* both many polls and half a second: the timer can step */
+    }
+    *abort_flag = 1;
+    if (atomicCAS(err, 0u, 2u) == 0u) err[1] = where;
+    return false;
+}
 __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap *map, unsigned bar, int x, int y, int z) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
@@ -115,14 +136,31 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32
                    "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
                  : "memory");
 }
+/* issued by a whole warp in uniform control flow: the operands are computed by all lanes (so that they can live in the
+ * uniform register file the instruction reads them from) and one elected lane issues */
+__device__ __forceinline__ void umma_f16_elect(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ta_elect(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_elect(unsigned bar) {
+    asm volatile("{\n .reg .pred e;\n elect.sync _|e, 0xffffffff;\n @e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) { float r; asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c)); return r; }
 __device__ __forceinline__ float ex2f(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __forceinline__ unsigned pack_h2(float lo, float hi) { unsigned r; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
 
 /* ---- pass 1: pages -> dense fp16 K [head][tok][128] and V^T [head][128][tok] ------------------- */
 template <int DT>
-__global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cache, int layer, int seq, int ntok, int tok_stride, __half *ws_k, __half *ws_vt) {
+__global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cache, int layer, int seq, int pg0, int ntok, int tok_stride, __half *ws_k, __half *ws_vt) {
     const hy3a_geom g = hy3a_make_geom(DT);
-    const int pg = blockIdx.x, hl = blockIdx.y, tid = threadIdx.x;
+    const int pg = pg0 + blockIdx.x, hl = blockIdx.y, tid = threadIdx.x;
+    /* programmatic dependent launch: the appended rows must be complete; the attention kernel may set itself up */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int block = cache.block_table[(size_t)seq * cache.max_blocks_per_seq + pg];
     const uint8_t *page = cache.pool + hy3a_page_index(cache, block, layer, hl) * (size_t)cache.page_bytes;
     const __half *ks = reinterpret_cast<const __half *>(page + g.ks_off), *vs = reinterpret_cast<const __half *>(page + g.vs_off);
@@ -184,7 +222,14 @@ struct prefill_args {
     size_t out_stride;
     int base, nq, kv_head_begin;
     unsigned *err;
+    unsigned long long *trace;   /* trace builds: time stamps of one CTA, [step][tile][8 events] */
 };
+#ifdef HY3A_DECODE_TRACE
+__device__ __forceinline__ unsigned long long pf_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define PF_TRACE(j, x, ev) do { if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (j) < 64) a.trace[((j) * 2 + (x)) * 8 + (ev)] = pf_gtime(); } while (0)
+#else
+#define PF_TRACE(j, x, ev) do { } while (0)
+#endif
 
 /* ---- pass 2: the attention kernel -------------------------------------------------------------- */
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -398,12 +443,12 @@ hy3a_prefill_kernel_v1(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
 /* ---- pass 2, second generation: two Q tiles per CTA and P in tensor memory ---------------------------------------
  * One CTA = 32 query tokens x the 8 query heads of one KV head = two 128-row Q tiles, A and B, that share every K/V
- * tile.  Each tile has its own softmax warpgroup (warps 0-3: A, 4-7: B), its own S (128 TMEM columns) and its own
- * O (128 columns): 512 columns in all.  While warpgroup A runs the softmax of its S_j, the tensor core computes
- * S_j of tile B, then P_A.V_j and S_A for tile j+1, and so on: the softmax of one tile hides behind the MMAs of the
- * other.  P never touches shared memory: the softmax threads write it as packed fp16 pairs over the first 64 columns
- * of their S (tcgen05.st) and P.V reads its A operand from tensor memory.  That frees 64 KB of shared memory, which
- * keeps K and V double-buffered beside the two Q tiles.                                                         */
+ * tile.  Each tile has its own softmax warps, its own S (128 TMEM columns) and its own O (128 columns): 512 columns in
+ * all.  While the softmax of tile A runs, the tensor core computes P_B.V_j and S_B for tile j+1, and so on: the
+ * softmax of one tile hides behind the MMAs of the other, and the single issuing warp's fixed order keeps the two
+ * tiles half a period out of phase.  P never touches shared memory: the softmax threads write it as packed fp16
+ * pairs over the first 64 columns of their S (tcgen05.st) and P.V reads its A operand from tensor memory.  That
+ * frees 64 KB of shared memory, which keeps K and V double-buffered beside the two Q tiles.                      */
 constexpr int kQTok2 = 32;                     /* query tokens per CTA = two tiles of kQTok */
 constexpr int kPf2SmWarps = 16;                /* softmax warps: tile x = warps with (warp / 4) % 2 == x; column half = warp / 8 */
 constexpr int kPf2Threads = 32 * kPf2SmWarps + 64;   /* + warp 16 = TMA producer, warp 17 = MMA issuer */
@@ -418,8 +463,8 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     uint8_t *sm = s_raw + ((1024u - (smem_u32(s_raw) & 1023u)) & 1023u);
     const unsigned sbase = smem_u32(sm);
     const unsigned bar0 = sbase + kOff2Bar;
-    volatile unsigned *s_tmem = reinterpret_cast<volatile unsigned *>(sm + kOff2Bar + 128);
-    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kOff2Bar + 132);
+    volatile unsigned *s_tmem = reinterpret_cast<volatile unsigned *>(sm + kOff2Bar + 192);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kOff2Bar + 196);
 #define BAR(i) (bar0 + 8u * (unsigned)(i))
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -431,13 +476,14 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         *s_abort = 0;
         mbar_init(BAR(B2_Q), 1);
         for (int i = 0; i < 2; i++) {
-            mbar_init(BAR(B2_KF + i), 1); mbar_init(BAR(B2_VF + i), 1); mbar_init(BAR(B2_KE + i), 1); mbar_init(BAR(B2_VE + i), 1);
+            mbar_init(BAR(B2_KF + i), 1); mbar_init(BAR(B2_VF + i), 1);
+            mbar_init(BAR(B2_KE + i), 1); mbar_init(BAR(B2_VE + i), 1);
             mbar_init(BAR(B2_SF + i), 1); mbar_init(BAR(B2_P + i), 256); mbar_init(BAR(B2_O + i), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {   /* one warp allocates all 512 TMEM columns (1 CTA per SM) */
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + kOff2Bar + 128), "r"(512u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + kOff2Bar + 192), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -449,6 +495,10 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (warp == kPf2SmWarps) {
         /* ===================== TMA producer ===================== */
         if (lane == 0) {
+            /* programmatic dependent launch: everything above ran beside the tail of the conversion kernel; the
+             * operands are complete from here on (all global reads of this CTA follow this thread's copies) */
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             mbar_expect_tx(BAR(B2_Q), 2 * kTileBytes);
             for (int x = 0; x < 2; x++) {
                 tma_load_3d(sbase + kOff2Q + x * kTileBytes, &tm_q, BAR(B2_Q), 0, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
@@ -456,11 +506,11 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
             for (int j = 0; j < ntiles; j++) {
                 const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
-                if (!mbar_wait(BAR(B2_KE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
+                if (!mbar_wait_blocking(BAR(B2_KE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
                 mbar_expect_tx(BAR(B2_KF + st), kTileBytes);
                 tma_load_3d(sbase + kOff2K + st * kTileBytes, &tm_k, BAR(B2_KF + st), 0, j * kKeys, hl);
                 tma_load_3d(sbase + kOff2K + st * kTileBytes + 16384, &tm_k, BAR(B2_KF + st), 64, j * kKeys, hl);
-                if (!mbar_wait(BAR(B2_VE + st), ph ^ 1u, s_abort, a.err, 11u)) break;
+                if (!mbar_wait_blocking(BAR(B2_VE + st), ph ^ 1u, s_abort, a.err, 11u)) break;
                 mbar_expect_tx(BAR(B2_VF + st), kTileBytes);
                 tma_load_3d(sbase + kOff2V + st * kTileBytes, &tm_v, BAR(B2_VF + st), j * kKeys, 0, hl);
                 tma_load_3d(sbase + kOff2V + st * kTileBytes + 16384, &tm_v, BAR(B2_VF + st), j * kKeys + 64, 0, hl);
@@ -469,59 +519,61 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     } else if (warp == kPf2SmWarps + 1) {
         /* ===================== MMA issuer =====================
          * order: S_A(0) S_B(0) | PV_A(0) S_A(1) | PV_B(0) S_B(1) | PV_A(1) S_A(2) | ...
-         * S_x(j+1) overwrites the columns P_x(j) lives in, so it is issued behind PV_x(j) (the tensor core runs in order) */
-        if (lane == 0) {
-            bool ok = mbar_wait(BAR(B2_Q), 0u, s_abort, a.err, 20u);
-            /* descriptors are computed once; inside the loops a k-step is one 64-bit add (the offsets stay inside the
-             * 14-bit address field: all tiles lie in the first 256 KB of shared memory) -- the scalar code between two
-             * tcgen05.mma of this lane is what bounds the issue rate */
-            const unsigned long long dQ[2] = {make_desc(sbase + kOff2Q), make_desc(sbase + kOff2Q + kTileBytes)};
-            const unsigned long long dK[2] = {make_desc(sbase + kOff2K), make_desc(sbase + kOff2K + kTileBytes)};
-            const unsigned long long dV[2] = {make_desc(sbase + kOff2V), make_desc(sbase + kOff2V + kTileBytes)};
-            auto issue_qk = [&](int x, int j) {      /* S_x(j) = Q_x . K_j^T : 8 k-steps of 16 over d = 128 */
-                const unsigned long long q = dQ[x], k = dK[j & 1];
-                const unsigned d = tmem + 128u * x;
+         * S_x(j+1) overwrites the columns P_x(j) lives in, so it is issued behind PV_x(j) (the tensor core runs in order).
+         * The whole warp runs this code in uniform control flow and one elected lane issues: the descriptors are then
+         * computed once per warp in the uniform data path that tcgen05.mma reads its operands from, and the scalar code
+         * between two MMAs -- which is what bounds the issue rate of one thread -- shrinks to an add per operand */
+        bool ok = mbar_wait_blocking(BAR(B2_Q), 0u, s_abort, a.err, 20u);
+        const unsigned long long dQ[2] = {make_desc(sbase + kOff2Q), make_desc(sbase + kOff2Q + kTileBytes)};
+        const unsigned long long dK[2] = {make_desc(sbase + kOff2K), make_desc(sbase + kOff2K + kTileBytes)};
+        const unsigned long long dV[2] = {make_desc(sbase + kOff2V), make_desc(sbase + kOff2V + kTileBytes)};
+        auto issue_qk = [&](int x, int j) {      /* S_x(j) = Q_x . K_j^T : 8 k-steps of 16 over d = 128 */
+            const unsigned long long q = dQ[x], k = dK[j & 1];
+            const unsigned d = tmem + 128u * x;
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) {
-                    const unsigned long long off = (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2);   /* (16 384 B | 32 B) >> 4 */
-                    umma_f16(d, q + off, k + off, kk > 0);
-                }
-                umma_commit(BAR(B2_SF + x));
-            };
-            if (ok) ok = mbar_wait(BAR(B2_KF), 0u, s_abort, a.err, 21u);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                issue_qk(0, 0);
-                issue_qk(1, 0);
-                umma_commit(BAR(B2_KE));
+            for (int kk = 0; kk < 8; kk++) {
+                const unsigned long long off = (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2);   /* (16 384 B | 32 B) >> 4 */
+                umma_f16_elect(d, q + off, k + off, kk > 0);
             }
-            for (int j = 0; j < ntiles && ok; j++) {
-                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
-                const int st1 = (j + 1) & 1; const unsigned ph1 = (unsigned)((j + 1) >> 1) & 1u;
-                for (int x = 0; x < 2 && ok; x++) {
-                    if (x == 0) ok = mbar_wait(BAR(B2_VF + st), ph, s_abort, a.err, 23u);
-                    if (ok) ok = mbar_wait(BAR(B2_P + x), (unsigned)j & 1u, s_abort, a.err, 24u);   /* P_x(j) in tensor memory, O_x rescaled */
-                    if (ok && j + 1 < ntiles && x == 0) ok = mbar_wait(BAR(B2_KF + st1), ph1, s_abort, a.err, 25u);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    /* O_x += P_x(j) . V_j : 8 k-steps of 16 keys; A = 8 columns of packed fp16 pairs per step */
-                    {
-                        const unsigned long long v = dV[st];
-                        const unsigned d = tmem + 256u + 128u * x, pa = tmem + 128u * x;
-                        const unsigned acc0 = j > 0 ? 1u : 0u;
+            umma_commit_elect(BAR(B2_SF + x));
+        };
+        if (ok) ok = mbar_wait_blocking(BAR(B2_KF), 0u, s_abort, a.err, 21u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_qk(0, 0);
+            issue_qk(1, 0);
+            umma_commit_elect(BAR(B2_KE));
+        }
+        for (int j = 0; j < ntiles && ok; j++) {
+            const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
+            const int st1 = (j + 1) & 1; const unsigned ph1 = (unsigned)((j + 1) >> 1) & 1u;
+            for (int x = 0; x < 2 && ok; x++) {
+                if (x == 0) ok = mbar_wait_blocking(BAR(B2_VF + st), ph, s_abort, a.err, 23u);
+                if (ok) ok = mbar_wait_blocking(BAR(B2_P + x), (unsigned)j & 1u, s_abort, a.err, 24u);   /* P_x(j) in tensor memory, O_x rescaled */
+                if (ok && j + 1 < ntiles && x == 0) ok = mbar_wait_blocking(BAR(B2_KF + st1), ph1, s_abort, a.err, 25u);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (lane == 0) PF_TRACE(j, x, 6);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                /* O_x += P_x(j) . V_j : 8 k-steps of 16 keys; A = 8 columns of packed fp16 pairs per step */
+                {
+                    const unsigned long long v = dV[st];
+                    const unsigned d = tmem + 256u + 128u * x, pa = tmem + 128u * x;
+                    const unsigned acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
-                        for (int kk = 0; kk < 8; kk++) {
-                            const unsigned long long off = (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2);
-                            umma_f16_ta(d, pa + 8u * kk, v + off, kk > 0 ? 1u : acc0);
-                        }
-                    }
-                    umma_commit(BAR(B2_O + x));
-                    if (x == 1) umma_commit(BAR(B2_VE + st));
-                    if (j + 1 < ntiles) {
-                        issue_qk(x, j + 1);
-                        if (x == 1) umma_commit(BAR(B2_KE + st1));
+                    for (int kk = 0; kk < 8; kk++) {
+                        const unsigned long long off = (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2);
+                        umma_f16_ta_elect(d, pa + 8u * kk, v + off, kk > 0 ? 1u : acc0);
                     }
                 }
+                umma_commit_elect(BAR(B2_O + x));
+                if (x == 1) umma_commit_elect(BAR(B2_VE + st));
+                if (j + 1 < ntiles) {
+                    issue_qk(x, j + 1);
+                    if (x == 1) umma_commit_elect(BAR(B2_KE + st1));
+                }
+                if (lane == 0) PF_TRACE(j, x, 7);
             }
         }
     } else {
@@ -537,7 +589,9 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         float m = -INFINITY, l = 0.f;    /* l: this thread's half of the row's denominator */
         bool ok = true;
         for (int j = 0; j < ntiles && ok; j++) {
-            ok = __all_sync(0xffffffffu, mbar_wait(BAR(B2_SF + x), (unsigned)j & 1u, s_abort, a.err, 30u));   /* keep the warp together */
+            ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B2_SF + x), (unsigned)j & 1u, s_abort, a.err, 30u));   /* keep the warp together */
+            const bool tr = (warp & 11) == 0 && lane == 0;   /* trace builds: the first warp of each tile */
+            if (tr) PF_TRACE(j, x, 0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int k0 = j * kKeys + 64 * hf;                    /* first key of this thread's columns */
             const bool masked = (j * kKeys + kKeys - 1 > a.base + tq0);   /* the tile crosses the diagonal of some row */
@@ -545,47 +599,46 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tmem_ld32_nowait(tm_s + lane_base + 64u * hf, v0);
             tmem_ld32_nowait(tm_s + lane_base + 64u * hf + 32u, v1);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (tr) PF_TRACE(j, x, 1);
+            /* the maximum is taken over the raw scores (the scale is positive) and the scale is folded into the exponent's
+             * argument: one FFMA per element instead of a multiply and a subtract */
             float mx = -INFINITY;
             if (masked) {      /* only the tiles on the diagonal pay for the causal test */
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
-                    float s0 = __uint_as_float(v0[i]) * kScaleLog2, s1 = __uint_as_float(v1[i]) * kScaleLog2;
-                    if (k0 + i > qpos) s0 = -INFINITY;
-                    if (k0 + 32 + i > qpos) s1 = -INFINITY;
-                    v0[i] = __float_as_uint(s0); v1[i] = __float_as_uint(s1);
-                    mx = fmaxf(mx, fmaxf(s0, s1));
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float s0 = __uint_as_float(v0[i]) * kScaleLog2, s1 = __uint_as_float(v1[i]) * kScaleLog2;
-                    v0[i] = __float_as_uint(s0); v1[i] = __float_as_uint(s1);
-                    mx = fmaxf(mx, fmaxf(s0, s1));
+                    if (k0 + i > qpos) v0[i] = 0xff800000u;
+                    if (k0 + 32 + i > qpos) v1[i] = 0xff800000u;
                 }
             }
+#pragma unroll
+            for (int i = 0; i < 32; i++) mx = fmax3(mx, __uint_as_float(v0[i]), __uint_as_float(v1[i]));
             xch[hf * 128 + r] = mx;
             asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
-            mx = fmaxf(mx, xch[(hf ^ 1) * 128 + r]);
+            mx = fmaxf(mx, xch[(hf ^ 1) * 128 + r]) * kScaleLog2;
+            if (tr) PF_TRACE(j, x, 2);
             const bool grow = mx > m + kPfThreshold;              /* true while m == -inf (key 0 is never masked) */
             const float m_new = grow ? mx : m;
+            const float neg_m = -m_new;
             unsigned pk[32];
             float lsum = 0.f;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
                 /* the denominator sums the unrounded values: the fp16 rounding of P is a zero-mean 2^-12 relative error per
                  * term, far below the tolerance */
-                const float e0 = ex2f(__uint_as_float(v0[i]) - m_new), e1 = ex2f(__uint_as_float(v0[i + 1]) - m_new);
-                const float e2 = ex2f(__uint_as_float(v1[i]) - m_new), e3 = ex2f(__uint_as_float(v1[i + 1]) - m_new);
+                const float e0 = ex2f(fmaf(__uint_as_float(v0[i]), kScaleLog2, neg_m)), e1 = ex2f(fmaf(__uint_as_float(v0[i + 1]), kScaleLog2, neg_m));
+                const float e2 = ex2f(fmaf(__uint_as_float(v1[i]), kScaleLog2, neg_m)), e3 = ex2f(fmaf(__uint_as_float(v1[i + 1]), kScaleLog2, neg_m));
                 pk[i >> 1] = pack_h2(e0, e1); pk[16 + (i >> 1)] = pack_h2(e2, e3);
                 lsum += (e0 + e1) + (e2 + e3);
             }
+            if (tr) PF_TRACE(j, x, 3);
             /* O_x is only ours again when P_x(j-1).V_(j-1) has completed */
             if (j > 0 && ok) {
-                ok = __all_sync(0xffffffffu, mbar_wait(BAR(B2_O + x), (unsigned)(j - 1) & 1u, s_abort, a.err, 31u));
+                ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B2_O + x), (unsigned)(j - 1) & 1u, s_abort, a.err, 31u));
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
             /* tcgen05.ld / .st are warp-collective: the whole warp rescales its 32 rows (this thread: 64 of the 128 output
              * dims) as soon as one of them moved its reference (the others multiply by exactly 1) */
+            if (tr) PF_TRACE(j, x, 4);
             const float alpha = grow ? ex2f(m - m_new) : 1.f;     /* 0 on the first tile (m = -inf) */
             if (__any_sync(0xffffffffu, grow)) {
                 l *= alpha;
@@ -608,12 +661,13 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(BAR(B2_P + x));
+            if (tr) PF_TRACE(j, x, 5);
         }
         /* epilogue: O / l, l = sum of the two halves */
         xch[512 + hf * 128 + r] = l;
         asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
         l += xch[512 + (hf ^ 1) * 128 + r];
-        if (ok && ntiles > 0) ok = mbar_wait(BAR(B2_O + x), (unsigned)(ntiles - 1) & 1u, s_abort, a.err, 32u);
+        if (ok && ntiles > 0) ok = mbar_wait_blocking(BAR(B2_O + x), (unsigned)(ntiles - 1) & 1u, s_abort, a.err, 32u);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (__all_sync(0xffffffffu, ok) && ntiles > 0) {      /* warp-uniform: tcgen05.ld is warp-collective */
             const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -675,29 +729,72 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
     const int kvh = ctx->cfg.kv_head_count;
     const int ntok = base_slot + nq;
     const int pages = (ntok + HY3A_PT - 1) / HY3A_PT;
-    const int tok_stride = pages * HY3A_PT;
-    /* fp16 workspace for this layer's K and V^T (grow-only, in steps of 1024 tokens) */
-    const size_t need = (size_t)kvh * (((size_t)tok_stride + 1023) / 1024 * 1024) * HY3A_D * sizeof(__half);
-    if (need > ctx->pf_bytes) {
-        HY3A_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v);
-        ctx->d_pf_k = ctx->d_pf_v = NULL; ctx->pf_bytes = 0;
-        if (cudaMalloc(&ctx->d_pf_k, need) != cudaSuccess || cudaMalloc(&ctx->d_pf_v, need) != cudaSuccess) {
-            cudaFree(ctx->d_pf_k); ctx->d_pf_k = NULL;
-            return hy3a_fail(ctx, HY3A_ENOMEM, "prefill: cannot allocate 2 x %zu bytes of fp16 workspace", need);
+    int tok_stride = pages * HY3A_PT, pg0 = 0;
+    void *ws_k = NULL, *ws_v = NULL;
+    /* 1st choice: this layer's operand mirror -- only the pages written since the last chunk are converted */
+    if (ctx->pf_mbudget) {
+        if (ctx->pf_mseq != seq) { for (int l = 0; l < ctx->cfg.n_layers; l++) ctx->pf_mntok[l] = 0; ctx->pf_mseq = seq; }
+        const int want = (tok_stride + 1023) / 1024 * 1024;
+        if (want > ctx->pf_mcap[layer]) {
+            const int seq_cap = (ctx->cfg.max_blocks_per_seq * HY3A_PT + 1023) / 1024 * 1024;
+            int cap = 2 * ctx->pf_mcap[layer];
+            if (cap > seq_cap) cap = seq_cap;
+            if (cap < want) cap = want;
+            const size_t old_b = 2 * (size_t)kvh * ctx->pf_mcap[layer] * HY3A_D * sizeof(__half), new_b = 2 * (size_t)kvh * cap * HY3A_D * sizeof(__half);
+            if (ctx->pf_mbytes - old_b + new_b <= ctx->pf_mbudget) {
+                HY3A_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+                cudaFree(ctx->pf_mk[layer]); cudaFree(ctx->pf_mv[layer]);
+                ctx->pf_mk[layer] = ctx->pf_mv[layer] = NULL; ctx->pf_mcap[layer] = 0; ctx->pf_mntok[layer] = 0; ctx->pf_mbytes -= old_b;
+                if (cudaMalloc(&ctx->pf_mk[layer], new_b / 2) == cudaSuccess && cudaMalloc(&ctx->pf_mv[layer], new_b / 2) == cudaSuccess) {
+                    ctx->pf_mcap[layer] = cap; ctx->pf_mbytes += new_b;
+                } else {
+                    cudaGetLastError();
+                    cudaFree(ctx->pf_mk[layer]); ctx->pf_mk[layer] = ctx->pf_mv[layer] = NULL;   /* fall through to the shared workspace */
+                }
+            }
         }
-        ctx->pf_bytes = need;
+        if (want <= ctx->pf_mcap[layer]) {
+            ws_k = ctx->pf_mk[layer]; ws_v = ctx->pf_mv[layer];
+            tok_stride = ctx->pf_mcap[layer];
+            pg0 = ctx->pf_mntok[layer] / HY3A_PT;          /* a partly filled page is converted again */
+            if (ctx->pf_mntok[layer] < ntok) ctx->pf_mntok[layer] = ntok;
+        }
+    }
+    /* 2nd choice: one workspace shared by all layers, rebuilt from the pages on every call (grow-only, in steps of
+     * 1024 tokens) */
+    if (!ws_k) {
+        const size_t need = (size_t)kvh * (((size_t)tok_stride + 1023) / 1024 * 1024) * HY3A_D * sizeof(__half);
+        if (need > ctx->pf_bytes) {
+            HY3A_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v);
+            ctx->d_pf_k = ctx->d_pf_v = NULL; ctx->pf_bytes = 0;
+            if (cudaMalloc(&ctx->d_pf_k, need) != cudaSuccess || cudaMalloc(&ctx->d_pf_v, need) != cudaSuccess) {
+                cudaFree(ctx->d_pf_k); ctx->d_pf_k = NULL;
+                return hy3a_fail(ctx, HY3A_ENOMEM, "prefill: cannot allocate 2 x %zu bytes of fp16 workspace", need);
+            }
+            ctx->pf_bytes = need;
+        }
+        ws_k = ctx->d_pf_k; ws_v = ctx->d_pf_v;
     }
     hy3a_cache_view cv = hy3a_view(ctx);
-    dim3 g1(pages, kvh);
-    switch (ctx->geom.dtype) {
-        case 3: hy3a_kv_to_f16_kernel<3><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
-        case 0: hy3a_kv_to_f16_kernel<0><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
-        case 1: hy3a_kv_to_f16_kernel<1><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
-        default: hy3a_kv_to_f16_kernel<2><<<g1, 256, 0, ctx->stream>>>(cv, layer, seq, ntok, tok_stride, (__half *)ctx->d_pf_k, (__half *)ctx->d_pf_v); break;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    if (pages > pg0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(pages - pg0, kvh); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = ctx->stream;
+        cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+        __half *wk = (__half *)ws_k, *wv = (__half *)ws_v;
+        cudaError_t e;
+        switch (ctx->geom.dtype) {
+            case 3: e = cudaLaunchKernelEx(&cfg, hy3a_kv_to_f16_kernel<3>, cv, layer, seq, pg0, ntok, tok_stride, wk, wv); break;
+            case 0: e = cudaLaunchKernelEx(&cfg, hy3a_kv_to_f16_kernel<0>, cv, layer, seq, pg0, ntok, tok_stride, wk, wv); break;
+            case 1: e = cudaLaunchKernelEx(&cfg, hy3a_kv_to_f16_kernel<1>, cv, layer, seq, pg0, ntok, tok_stride, wk, wv); break;
+            default: e = cudaLaunchKernelEx(&cfg, hy3a_kv_to_f16_kernel<2>, cv, layer, seq, pg0, ntok, tok_stride, wk, wv); break;
+        }
+        ctx->launches++;
+        HY3A_CUDA(ctx, e);
     }
-    ctx->launches++;
-    HY3A_CUDA(ctx, cudaGetLastError());
 
     { const char *e = getenv("HY3A_PF_STOP"); if (e && atoi(e) == 1) return HY3A_OK; }   /* development: pass 1 only */
     CUtensorMap tq, tk, tv;
@@ -708,11 +805,11 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
         if (rc) return rc;
         const cuuint64_t dk[3] = {HY3A_D, (cuuint64_t)tok_stride, (cuuint64_t)kvh}, sk[2] = {HY3A_D * 2, (cuuint64_t)tok_stride * HY3A_D * 2};
         const cuuint32_t bk[3] = {64, kKeys, 1};
-        rc = make_map(ctx, &tk, ctx->d_pf_k, dk, sk, bk);
+        rc = make_map(ctx, &tk, ws_k, dk, sk, bk);
         if (rc) return rc;
         const cuuint64_t dv[3] = {(cuuint64_t)tok_stride, HY3A_D, (cuuint64_t)kvh}, sv[2] = {(cuuint64_t)tok_stride * 2, (cuuint64_t)tok_stride * HY3A_D * 2};
         const cuuint32_t bv[3] = {64, HY3A_D, 1};
-        rc = make_map(ctx, &tv, ctx->d_pf_v, dv, sv, bv);
+        rc = make_map(ctx, &tv, ws_v, dv, sv, bv);
         if (rc) return rc;
     }
     static bool attr_dev[64];   /* function attributes are per device */
@@ -723,14 +820,16 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
         attr_set = true;
     }
     prefill_args a;
-    a.out = out; a.out_stride = out_stride; a.base = base_slot; a.nq = nq; a.kv_head_begin = ctx->cfg.kv_head_begin; a.err = ctx->d_err;
+    a.out = out; a.out_stride = out_stride; a.base = base_slot; a.nq = nq; a.kv_head_begin = ctx->cfg.kv_head_begin; a.err = ctx->d_err; a.trace = ctx->d_trace;
     const char *v1 = getenv("HY3A_PF_V1");   /* first-generation kernel: one Q tile per CTA, P through shared memory */
     if (v1 && atoi(v1)) {
         dim3 g2((nq + kQTok - 1) / kQTok, kvh);
         hy3a_prefill_kernel_v1<<<g2, kPfThreads, kPfSmem, ctx->stream>>>(tq, tk, tv, a);
     } else {
-        dim3 g2((nq + kQTok2 - 1) / kQTok2, kvh);
-        hy3a_prefill_kernel<<<g2, kPf2Threads, kPf2Smem, ctx->stream>>>(tq, tk, tv, a);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((nq + kQTok2 - 1) / kQTok2, kvh); cfg.blockDim = dim3(kPf2Threads); cfg.dynamicSmemBytes = kPf2Smem; cfg.stream = ctx->stream;
+        cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+        HY3A_CUDA(ctx, cudaLaunchKernelEx(&cfg, hy3a_prefill_kernel, tq, tk, tv, a));
     }
     ctx->launches++;
     ctx->bulk_write_pending = 1;
