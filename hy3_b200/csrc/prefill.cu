@@ -7,22 +7,22 @@
  * queries see the cache's (quantised) K/V also for their own chunk (hy3_gpu.cu:823-832).
  *
  * Two kernels per (layer, chunk):
- *   1. hy3a_kv_to_f16_kernel<DT>: gathers the sequence's pages of this layer into a dense fp16
- *      workspace, dequantising INT8/INT4 (value = code * fp16 scale, hy3_gpu.cu:206-215): K as
- *      [head][token][128] (d contiguous) and V TRANSPOSED as [head][128][token] (tokens contiguous),
- *      so that both are K-major operands for the tensor cores.
- *   2. hy3a_prefill_kernel: one CTA per (16 query tokens x the 8 query heads of one KV head) = a
- *      128-row Q tile (GQA packing: the 8 heads share every K/V tile).  Warp-specialised:
- *        warp 4   TMA producer: Q once, then K_j / V_j tiles (128 keys) into 2-stage rings
- *                 (cp.async.bulk.tensor, 128-byte swizzle, mbarrier transaction counts)
- *        warp 5   MMA issuer (one elected lane): S_j = Q.K_j^T and O += P_j.V_j with
- *                 tcgen05.mma.cta_group::1.kind::f16, M=128 N=128 K=16, accumulators in TMEM
- *                 (S double-buffered: columns 0-127 / 128-255, O: columns 256-383);
- *                 tcgen05.commit signals mbarriers
- *        warps 0-3  softmax, one thread per row: tcgen05.ld the row of S, online softmax in base 2
- *                 with a lazily updated reference max, P_j as fp16 into shared memory in the
- *                 tensor core's swizzled K-major layout, conditional rescale of O in TMEM
- *                 (tcgen05.ld / tcgen05.st); epilogue O / l -> fp32 output.
+ *   1. hy3a_kv_to_f16_kernel<DT>: converts the sequence's pages of this layer into dense fp16 operands,
+ *      dequantising INT8/INT4 (value = code * fp16 scale, hy3_gpu.cu:206-215): K as [head][token][128]
+ *      (d contiguous) and V TRANSPOSED as [head][128][token] (tokens contiguous), so that both are
+ *      K-major operands for the tensor cores.  The operands of a layer are kept across chunks (the
+ *      context's per-layer mirrors), so a chunk only converts the pages it appended.
+ *   2. hy3a_prefill_kernel: one CTA per (32 query tokens x the 8 query heads of one KV head) = two
+ *      128-row Q tiles (GQA packing: the 8 heads share every K/V tile).  Warp-specialised:
+ *        TMA producer: Q once, then 64-key K / V tiles into 4-stage rings (cp.async.bulk.tensor,
+ *                 128-byte swizzle, mbarrier transaction counts)
+ *        MMA issuers (one warp per Q tile, one elected lane): S = Q.K^T (M=128, N=64, K=16) and
+ *                 O += P.V (N=128) with tcgen05.mma.cta_group::1.kind::f16, accumulators in TMEM
+ *                 (per Q tile two S buffers of 64 columns and O of 128); tcgen05.commit signals mbarriers
+ *        softmax warps, one thread per row: tcgen05.ld the row of S, online softmax in base 2 with a
+ *                 lazily updated reference max, P as packed fp16 over the S columns (tcgen05.st; P.V
+ *                 reads its A operand from tensor memory), conditional rescale of O in TMEM;
+ *                 epilogue O / l -> fp32 output.
  *      Causal masking only touches the tiles that cross the diagonal.
  *
  * Every wait is bounded; a wait that runs out raises a CTA-wide abort flag, records a code in the
@@ -43,12 +43,6 @@ namespace {
 constexpr int kQTok = 16;            /* query tokens per CTA (x 8 heads = 128 rows) */
 constexpr int kKeys = 128;           /* keys per K/V tile */
 constexpr int kTileBytes = 128 * 128 * 2;   /* one 128x128 fp16 operand tile = two 16 KB swizzled sub-tiles */
-constexpr int kPfThreads = 192;
-/* shared memory map (bytes from a 1024-aligned base) */
-constexpr int kOffQ = 0, kOffK = kOffQ + kTileBytes, kOffV = kOffK + 2 * kTileBytes, kOffP = kOffV + 2 * kTileBytes;
-constexpr int kOffBar = kOffP + kTileBytes;          /* 16 mbarriers + tmem address + abort flag */
-constexpr int kPfSmem = kOffBar + 256 + 1024;        /* + slack for the 1024-byte alignment */
-enum { BAR_Q = 0, BAR_KF = 1, BAR_VF = 3, BAR_KE = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_P = 13, BAR_O = 14 };
 constexpr float kScaleLog2 = 0.08838834764831845f * 1.4426950408889634f;   /* 1/sqrt(128) * log2(e) */
 constexpr float kPfThreshold = 8.f;
 
@@ -61,19 +55,8 @@ __device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
     asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-/* bounded wait, see the header comment */
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, unsigned *err, unsigned where) {
-    if (mbar_test(bar, parity)) return true;
-    for (unsigned i = 0; i < (1u << 22); i++) {
-        if (mbar_test(bar, parity)) return true;
-        if ((i & 63u) == 63u) { if (*abort_flag) return false; __nanosleep(32); }
-    }
-    *abort_flag = 1;
-    if (atomicCAS(err, 0u, 2u) == 0u) err[1] = where;
-    return false;
-}
-/* the same bound with mbarrier.try_wait, which suspends the thread until the phase completes or the hint elapses: the
- * waiter wakes within tens of ns of the arrival instead of at its next poll */
+/* bounded wait, see the header comment: mbarrier.try_wait suspends the thread until the phase completes or the hint elapses,
+ * so the waiter wakes within tens of ns of the arrival */
 __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity, unsigned hint_ns) {
     unsigned ok;
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
@@ -104,18 +87,6 @@ __device__ __forceinline__ unsigned long long make_desc(unsigned saddr) {
 }
 /* instruction descriptor: D = f32 (bit 4), A = B = f16 (0), both K-major, N = 128 (>>3 at bit 17), M = 128 (>>4 at bit 24) */
 constexpr unsigned kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-__device__ __forceinline__ void umma_f16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
-}
-/* A operand in tensor memory (lane = row, 32-bit column c holds elements 2c and 2c+1 of the row's K slice) */
-__device__ __forceinline__ void umma_f16_ta(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
@@ -142,6 +113,7 @@ __device__ __forceinline__ void umma_f16_elect(unsigned d_tmem, unsigned long lo
     asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
 }
+/* A operand in tensor memory (lane = row, 32-bit column c holds elements 2c and 2c+1 of the row's K slice) */
 __device__ __forceinline__ void umma_f16_ta_elect(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned accumulate) {
     asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
@@ -227,219 +199,13 @@ struct prefill_args {
 #ifdef HY3A_DECODE_TRACE
 __device__ __forceinline__ unsigned long long pf_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #define PF_TRACE(j, x, ev) do { if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (j) < 64) a.trace[((j) * 2 + (x)) * 8 + (ev)] = pf_gtime(); } while (0)
+#define PF_TRACE2(j, x, ev) do { if (lane == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (j) < 64) a.trace[1024 + ((j) * 2 + (x)) * 4 + (ev)] = pf_gtime(); } while (0)
+#define PF_TRACE3(j, x, ev) do { if (lane == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (j) < 64) a.trace[2048 + ((j) * 2 + (x)) * 2 + (ev)] = pf_gtime(); } while (0)
 #else
 #define PF_TRACE(j, x, ev) do { } while (0)
+#define PF_TRACE2(j, x, ev) do { } while (0)
+#define PF_TRACE3(j, x, ev) do { } while (0)
 #endif
-
-/* ---- pass 2: the attention kernel -------------------------------------------------------------- */
-__global__ void __launch_bounds__(kPfThreads, 1)
-hy3a_prefill_kernel_v1(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
-    extern __shared__ uint8_t s_raw[];
-    uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~(uintptr_t)1023);
-    const unsigned sbase = smem_u32(sm);
-    const unsigned bar0 = sbase + kOffBar;
-    volatile unsigned *s_tmem = reinterpret_cast<volatile unsigned *>(sm + kOffBar + 128);
-    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kOffBar + 132);
-#define BAR(i) (bar0 + 8u * (unsigned)(i))
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q0 = blockIdx.x * kQTok, hl = blockIdx.y;
-    const int kv_end = min(a.base + q0 + kQTok, a.base + a.nq);   /* keys [0, kv_end) matter for this tile */
-    const int ntiles = (kv_end + kKeys - 1) / kKeys;
-
-    if (tid == 0) {
-        *s_abort = 0;
-        mbar_init(BAR(BAR_Q), 1);
-        for (int i = 0; i < 2; i++) {
-            mbar_init(BAR(BAR_KF + i), 1); mbar_init(BAR(BAR_VF + i), 1); mbar_init(BAR(BAR_KE + i), 1); mbar_init(BAR(BAR_VE + i), 1);
-            mbar_init(BAR(BAR_SF + i), 1); mbar_init(BAR(BAR_SE + i), 128);
-        }
-        mbar_init(BAR(BAR_P), 128);
-        mbar_init(BAR(BAR_O), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {   /* one warp allocates all 512 TMEM columns (1 CTA per SM) */
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + kOffBar + 128), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const unsigned tmem = *s_tmem;
-    const unsigned tm_s[2] = {tmem, tmem + 128u}, tm_o = tmem + 256u;
-
-    if (warp == 4) {
-        /* ===================== TMA producer ===================== */
-        if (lane == 0) {
-            mbar_expect_tx(BAR(BAR_Q), kTileBytes);
-            tma_load_3d(sbase + kOffQ, &tm_q, BAR(BAR_Q), 0, (a.kv_head_begin + hl) * 8, q0);
-            tma_load_3d(sbase + kOffQ + 16384, &tm_q, BAR(BAR_Q), 64, (a.kv_head_begin + hl) * 8, q0);
-            for (int j = 0; j < ntiles; j++) {
-                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
-                if (!mbar_wait(BAR(BAR_KE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
-                mbar_expect_tx(BAR(BAR_KF + st), kTileBytes);
-                tma_load_3d(sbase + kOffK + st * kTileBytes, &tm_k, BAR(BAR_KF + st), 0, j * kKeys, hl);
-                tma_load_3d(sbase + kOffK + st * kTileBytes + 16384, &tm_k, BAR(BAR_KF + st), 64, j * kKeys, hl);
-                if (!mbar_wait(BAR(BAR_VE + st), ph ^ 1u, s_abort, a.err, 11u)) break;
-                mbar_expect_tx(BAR(BAR_VF + st), kTileBytes);
-                tma_load_3d(sbase + kOffV + st * kTileBytes, &tm_v, BAR(BAR_VF + st), j * kKeys, 0, hl);
-                tma_load_3d(sbase + kOffV + st * kTileBytes + 16384, &tm_v, BAR(BAR_VF + st), j * kKeys + 64, 0, hl);
-            }
-        }
-    } else if (warp == 5) {
-        /* ===================== MMA issuer ===================== */
-        if (lane == 0) {
-            bool ok = mbar_wait(BAR(BAR_Q), 0u, s_abort, a.err, 20u);
-            /* S_j = Q . K_j^T : 8 k-steps of 16 over d = 128 (two swizzled 64-wide sub-tiles) */
-            auto issue_qk = [&](int j) {
-                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
-                if (!mbar_wait(BAR(BAR_KF + st), ph, s_abort, a.err, 21u)) return false;
-                if (!mbar_wait(BAR(BAR_SE + st), ph ^ 1u, s_abort, a.err, 22u)) return false;   /* S buffer read out by the softmax warps */
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int kk = 0; kk < 8; kk++) {
-                    const unsigned off = (unsigned)(kk >> 2) * 16384u + (unsigned)(kk & 3) * 32u;
-                    umma_f16(tm_s[st], make_desc(sbase + kOffQ + off), make_desc(sbase + kOffK + st * kTileBytes + off), kk > 0);
-                }
-                umma_commit(BAR(BAR_SF + st));   /* S_j ready */
-                umma_commit(BAR(BAR_KE + st));   /* K stage free */
-                return true;
-            };
-            if (ok) ok = issue_qk(0);
-            for (int j = 0; j < ntiles && ok; j++) {
-                if (j + 1 < ntiles) ok = issue_qk(j + 1);
-                if (!ok) break;
-                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
-                if (!mbar_wait(BAR(BAR_VF + st), ph, s_abort, a.err, 23u)) break;
-                if (!mbar_wait(BAR(BAR_P), (unsigned)j & 1u, s_abort, a.err, 24u)) break;       /* P_j written (and O rescaled) */
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                /* O += P_j . V_j : 8 k-steps of 16 over the 128 keys */
-#pragma unroll
-                for (int kk = 0; kk < 8; kk++) {
-                    const unsigned off = (unsigned)(kk >> 2) * 16384u + (unsigned)(kk & 3) * 32u;
-                    umma_f16(tm_o, make_desc(sbase + kOffP + off), make_desc(sbase + kOffV + st * kTileBytes + off), (j > 0 || kk > 0));
-                }
-                umma_commit(BAR(BAR_O));          /* O updated, P buffer free */
-                umma_commit(BAR(BAR_VE + st));    /* V stage free */
-            }
-        }
-    } else {
-        /* ===================== softmax warps 0-3: thread = row of the Q tile ===================== */
-        const int r = tid, t_local = r >> 3, h = r & 7;
-        const int qpos = a.base + q0 + t_local;                 /* global index of this row's query */
-        const bool row_valid = (q0 + t_local) < a.nq;
-        const unsigned lane_base = (unsigned)(warp * 32) << 16; /* this warp's quarter of the TMEM lanes */
-        float m = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int j = 0; j < ntiles && ok; j++) {
-            const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(BAR(BAR_SF + st), ph, s_abort, a.err, 30u));   /* keep the warp together */
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int k0 = j * kKeys;
-            const bool masked = (k0 + kKeys - 1 > a.base + q0);   /* the tile crosses the diagonal of some row */
-            /* pass 1: row max */
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                unsigned v[32];
-                tmem_ld32(tm_s[st] + lane_base + 32u * c, v);
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float s = __uint_as_float(v[i]) * kScaleLog2;
-                    if (masked && k0 + 32 * c + i > qpos) s = -INFINITY;
-                    mx = fmaxf(mx, s);
-                }
-            }
-            const bool grow = mx > m + kPfThreshold;              /* true while m == -inf (key 0 is never masked) */
-            const float m_new = grow ? mx : m;
-            /* pass 2: P = 2^(s - m) as fp16 pairs, l from the rounded values */
-            unsigned pk[64];
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                unsigned v[32];
-                tmem_ld32(tm_s[st] + lane_base + 32u * c, v);
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float s0 = __uint_as_float(v[i]) * kScaleLog2, s1 = __uint_as_float(v[i + 1]) * kScaleLog2;
-                    if (masked && k0 + 32 * c + i > qpos) s0 = -INFINITY;
-                    if (masked && k0 + 32 * c + i + 1 > qpos) s1 = -INFINITY;
-                    const unsigned p2 = pack_h2(ex2f(s0 - m_new), ex2f(s1 - m_new));
-                    pk[16 * c + (i >> 1)] = p2;
-                }
-            }
-            /* S_j is in registers: hand the buffer back to the tensor core */
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(BAR(BAR_SE + st));
-            float lsum = 0.f;
-#pragma unroll
-            for (int i = 0; i < 64; i++) { const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&pk[i])); lsum += f.x + f.y; }
-            /* O and the P buffer are only ours again when P_{j-1}.V_{j-1} has completed */
-            if (j > 0 && ok) {
-                ok = __all_sync(0xffffffffu, mbar_wait(BAR(BAR_O), (unsigned)(j - 1) & 1u, s_abort, a.err, 31u));
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            /* tcgen05.ld / .st are warp-collective: the whole warp rescales its 32 rows as soon as one of them
-             * moved its reference (the others multiply by exactly 1)                                          */
-            const float alpha = grow ? ex2f(m - m_new) : 1.f;     /* 0 on the first tile (m = -inf) */
-            if (__any_sync(0xffffffffu, grow)) {
-                l *= alpha;
-                if (j > 0) {
-#pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        unsigned v[32];
-                        tmem_ld32(tm_o + lane_base + 32u * c, v);
-#pragma unroll
-                        for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st32(tm_o + lane_base + 32u * c, v);
-                    }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                }
-                m = m_new;
-            }
-            l += lsum;
-            /* P row r into the swizzled K-major layout: 16-byte chunk c of sub-tile c/8 lands at chunk (c%8)^(r%8) */
-            {
-                uint8_t *prow = sm + kOffP + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll
-                for (int c = 0; c < 16; c++) {
-                    uint4 w = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-                    *reinterpret_cast<uint4 *>(prow + (c >> 3) * 16384 + (((c & 7) ^ (r & 7)) << 4)) = w;
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   /* generic-proxy writes -> visible to the tensor core */
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(BAR(BAR_P));
-        }
-        /* epilogue: O / l */
-        if (ok && ntiles > 0) ok = mbar_wait(BAR(BAR_O), (unsigned)(ntiles - 1) & 1u, s_abort, a.err, 32u);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__all_sync(0xffffffffu, ok) && ntiles > 0) {      /* warp-uniform: tcgen05.ld is warp-collective */
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            float *orow = a.out + (size_t)(q0 + t_local) * a.out_stride + (size_t)((a.kv_head_begin + hl) * 8 + h) * HY3A_D;
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                unsigned v[32];
-                tmem_ld32(tm_o + lane_base + 32u * c, v);
-                if (row_valid)
-#pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    *reinterpret_cast<float4 *>(orow + 32 * c + i) = make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
-                                                                                   __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-            }
-        }
-    }
-    /* ---- common exit: everybody arrives here, also after a wait ran out; release TMEM */
-    if (*s_abort && warp == 4 && lane == 0) {
-        /* copies already issued must land before the shared memory goes away */
-        for (int st = 0; st < 2; st++)
-            for (unsigned ph = 0; ph < 2; ph++)
-                for (unsigned spin = 0; spin < (1u << 12) && !mbar_test(BAR(BAR_KF + st), ph) && !mbar_test(BAR(BAR_VF + st), ph); spin++) __nanosleep(64);
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
-#undef BAR
-}
 
 /* ---- pass 2, second generation: two Q tiles per CTA and P in tensor memory ---------------------------------------
  * One CTA = 32 query tokens x the 8 query heads of one KV head = two 128-row Q tiles, A and B, that share every K/V
@@ -458,7 +224,7 @@ constexpr int kPf2Smem = kOff2Xch + 4096 + 1024;   /* maxima in the first 2 KB, 
 enum { B2_Q = 0, B2_KF = 1, B2_VF = 3, B2_KE = 5, B2_VE = 7, B2_SF = 9, B2_P = 11, B2_O = 13 };   /* [2] each except Q */
 
 __global__ void __launch_bounds__(kPf2Threads, 1)
-hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
+hy3a_prefill_kernel_v2(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
     extern __shared__ uint8_t s_raw[];
     uint8_t *sm = s_raw + ((1024u - (smem_u32(s_raw) & 1023u)) & 1023u);
     const unsigned sbase = smem_u32(sm);
@@ -697,6 +463,272 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #undef BAR
 }
 
+/* ---- pass 2, third generation: 64-key tiles, S double-buffered -------------------------------------------------------
+ * Same CTA shape as the second generation (two 128-row Q tiles A and B = 32 query tokens x 8 heads, P in tensor
+ * memory), but a K/V tile is 64 keys, so that each Q tile has TWO S buffers (2 x 64 TMEM columns) beside its O (128
+ * columns): 2 x 256 = 512 columns.  S_x(j+2) is issued right behind P_x(j).V_j into the buffer P_x(j) lives in, i.e. the
+ * scores of a step are computed while the softmax of the step before runs, and the loop
+ *      S ready -> softmax -> P -> P.V -> next S
+ * of the second generation, whose length bounded it, falls apart into a softmax chain (one thread per row, 64 columns
+ * per step, no exchange between threads) and an MMA chain that only meet at the P and S barriers.  The softmax warps
+ * wait for P.V only when a row's reference maximum moved (lazy rescale of O) and at the end.
+ * Warps 0-3 / 4-7: softmax of tile A / B; warp 8: TMA producer (4-stage rings of 16 KB K and V tiles); warps 9 / 10:
+ * MMA issuers of tile A / B, each in uniform control flow with one elected lane (one thread issues an MMA every
+ * ~26 ns at best, which a single issuer for both tiles would be bound by).                                       */
+constexpr int kKeys3 = 64;
+constexpr int kK3Bytes = kKeys3 * 128 * 2;      /* one K tile = two sub-tiles [64 keys][64 dims]; one V^T tile = [128 dims][64 keys] */
+constexpr int kSt3 = 4;                         /* ring stages */
+constexpr int kPf3Threads = 352;
+constexpr int kOff3Q = 0, kOff3K = kOff3Q + 2 * kTileBytes, kOff3V = kOff3K + kSt3 * kK3Bytes, kOff3Bar = kOff3V + kSt3 * kK3Bytes;
+constexpr int kPf3Smem = kOff3Bar + 512 + 1024;
+enum { B3_Q = 0, B3_KF = 1, B3_KE = 5, B3_VF = 9, B3_VE = 13, B3_SF = 17, B3_P = 21, B3_O = 25 };   /* KF..VE [4 stages]; SF, P [tile][buffer]; O [tile] */
+constexpr unsigned kIdescN64 = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+__device__ __forceinline__ void umma_f16_n64_elect(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdescN64), "r"(accumulate) : "memory");
+}
+
+__global__ void __launch_bounds__(kPf3Threads, 1)
+hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
+    extern __shared__ uint8_t s_raw[];
+    uint8_t *sm = s_raw + ((1024u - (smem_u32(s_raw) & 1023u)) & 1023u);
+    const unsigned sbase = smem_u32(sm);
+    const unsigned bar0 = sbase + kOff3Bar;
+    volatile unsigned *s_tmem = reinterpret_cast<volatile unsigned *>(sm + kOff3Bar + 256);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kOff3Bar + 260);
+#define BAR(i) (bar0 + 8u * (unsigned)(i))
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q0 = blockIdx.x * kQTok2, hl = blockIdx.y;
+    const int kv_end = min(a.base + q0 + kQTok2, a.base + a.nq);   /* keys [0, kv_end) matter for this CTA */
+    const int ntiles = (kv_end + kKeys3 - 1) / kKeys3;
+
+    if (tid == 0) {
+        *s_abort = 0;
+        mbar_init(BAR(B3_Q), 1);
+        for (int i = 0; i < kSt3; i++) { mbar_init(BAR(B3_KF + i), 1); mbar_init(BAR(B3_KE + i), 2); mbar_init(BAR(B3_VF + i), 1); mbar_init(BAR(B3_VE + i), 2); }   /* KE, VE: one commit per issuer */
+        for (int i = 0; i < 4; i++) { mbar_init(BAR(B3_SF + i), 1); mbar_init(BAR(B3_P + i), 4); }   /* P: one arrival per softmax warp of the tile */
+        mbar_init(BAR(B3_O), 1); mbar_init(BAR(B3_O + 1), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {   /* one warp allocates all 512 TMEM columns (1 CTA per SM) */
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + kOff3Bar + 256), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = *s_tmem;
+    /* tile x: S buffers at columns 128x and 128x + 64 (P over the first 32 columns of its S), O at columns 256 + 128x */
+
+    if (warp == 8) {
+        /* ===================== TMA producer ===================== */
+        if (lane == 0) {
+            /* programmatic dependent launch: everything above ran beside the tail of the conversion kernel; the
+             * operands are complete from here on (all global reads of this CTA follow this thread's copies) */
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+            mbar_expect_tx(BAR(B3_Q), 2 * kTileBytes);
+            for (int x = 0; x < 2; x++) {
+                tma_load_3d(sbase + kOff3Q + x * kTileBytes, &tm_q, BAR(B3_Q), 0, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
+                tma_load_3d(sbase + kOff3Q + x * kTileBytes + 16384, &tm_q, BAR(B3_Q), 64, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
+            }
+            /* K runs two tiles ahead of V: S_(j+2) is issued behind P_j.V_j */
+            for (int j = 0; j < ntiles + 2; j++) {
+                if (j < ntiles) {
+                    const int st = j & (kSt3 - 1); const unsigned ph = (unsigned)(j / kSt3) & 1u;
+                    if (!mbar_wait_blocking(BAR(B3_KE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
+                    mbar_expect_tx(BAR(B3_KF + st), kK3Bytes);
+                    tma_load_3d(sbase + kOff3K + st * kK3Bytes, &tm_k, BAR(B3_KF + st), 0, j * kKeys3, hl);
+                    tma_load_3d(sbase + kOff3K + st * kK3Bytes + 8192, &tm_k, BAR(B3_KF + st), 64, j * kKeys3, hl);
+                }
+                if (j >= 2) {
+                    const int jv = j - 2, st = jv & (kSt3 - 1); const unsigned ph = (unsigned)(jv / kSt3) & 1u;
+                    if (!mbar_wait_blocking(BAR(B3_VE + st), ph ^ 1u, s_abort, a.err, 11u)) break;
+                    mbar_expect_tx(BAR(B3_VF + st), kK3Bytes);
+                    tma_load_3d(sbase + kOff3V + st * kK3Bytes, &tm_v, BAR(B3_VF + st), jv * kKeys3, 0, hl);
+                }
+            }
+        }
+    } else if (warp >= 9) {
+        /* ===================== MMA issuer of tile x (whole warp, one elected lane issues) =====================
+         * order: S_x(0) S_x(1) | PV_x(0) S_x(2) | PV_x(1) S_x(3) | ...   tcgen05.commit covers what this thread issued, so
+         * a K or V stage is released by one commit of each issuer */
+        const int x = warp - 9;
+        bool ok = mbar_wait_blocking(BAR(B3_Q), 0u, s_abort, a.err, 20u);
+        const unsigned long long dQ = make_desc(sbase + kOff3Q + x * kTileBytes);
+        const unsigned long long dK0 = make_desc(sbase + kOff3K), dV0 = make_desc(sbase + kOff3V);
+        const unsigned tm_sx = tmem + 128u * x, tm_ox = tmem + 256u + 128u * x;
+        auto issue_qk = [&](int j) {      /* S_x(j) = Q_x . K_j^T into buffer j & 1: 8 k-steps of 16 over d = 128 */
+            const unsigned long long k = dK0 + (unsigned long long)((j & (kSt3 - 1)) * (kK3Bytes >> 4));
+            const unsigned d = tm_sx + 64u * (j & 1);
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++)      /* the second half of d lies one sub-tile further on: 16 KB for Q, 8 KB for K */
+                umma_f16_n64_elect(d, dQ + (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2), k + (unsigned long long)((kk >> 2) * 512 + (kk & 3) * 2), kk > 0);
+            umma_commit_elect(BAR(B3_SF + 2 * x + (j & 1)));
+            umma_commit_elect(BAR(B3_KE + (j & (kSt3 - 1))));
+        };
+        /* tile B starts when the first softmax of tile A is through: half a period out of phase, the MMAs of one tile
+         * run while the other tile's issuer is between two steps and its softmax warps have the SM's exponential
+         * unit to themselves (nothing pulls the two loops apart by itself when they start together) */
+        if (ok && x == 1) ok = mbar_wait_blocking(BAR(B3_P + 0), 0u, s_abort, a.err, 22u);
+        for (int j = 0; j < 2 && j < ntiles && ok; j++) {
+            ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B3_KF + j), 0u, s_abort, a.err, 21u));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_qk(j);
+        }
+        for (int j = 0; j < ntiles && ok; j++) {
+            const int st = j & (kSt3 - 1); const unsigned ph = (unsigned)(j / kSt3) & 1u;
+            const int j2 = j + 2, st2 = j2 & (kSt3 - 1); const unsigned ph2 = (unsigned)(j2 / kSt3) & 1u;
+            PF_TRACE2(j, x, 0);
+            ok = mbar_wait_blocking(BAR(B3_VF + st), ph, s_abort, a.err, 23u);
+            PF_TRACE2(j, x, 1);
+            if (ok && j2 < ntiles) ok = mbar_wait_blocking(BAR(B3_KF + st2), ph2, s_abort, a.err, 25u);
+            PF_TRACE2(j, x, 2);
+            if (ok) ok = mbar_wait_blocking(BAR(B3_P + 2 * x + (j & 1)), (unsigned)(j >> 1) & 1u, s_abort, a.err, 24u);   /* P_x(j) in tensor memory, O_x rescaled */
+            PF_TRACE2(j, x, 3);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane == 0) PF_TRACE(j, x, 6);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            /* O_x += P_x(j) . V_j : 4 k-steps of 16 keys; A = 8 columns of packed fp16 pairs per step */
+            {
+                const unsigned long long v = dV0 + (unsigned long long)(st * (kK3Bytes >> 4));
+                const unsigned pa = tm_sx + 64u * (j & 1);
+                const unsigned acc0 = j > 0 ? 1u : 0u;
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) umma_f16_ta_elect(tm_ox, pa + 8u * kk, v + (unsigned long long)(kk * 2), kk > 0 ? 1u : acc0);
+            }
+            PF_TRACE3(j, x, 0);
+            umma_commit_elect(BAR(B3_O + x));
+            umma_commit_elect(BAR(B3_VE + st));
+            PF_TRACE3(j, x, 1);
+            if (j2 < ntiles) issue_qk(j2);
+            if (lane == 0) PF_TRACE(j, x, 7);
+        }
+    } else {
+        /* ===================== softmax warps: tile x = warp / 4; thread = one row of Q tile x ===================== */
+        const int x = warp >> 2, r = tid & 127, t_local = r >> 3, h = r & 7;
+        const int tq0 = q0 + x * kQTok;                          /* first query token of this tile */
+        const int qpos = a.base + tq0 + t_local;                 /* global index of this row's query */
+        const bool row_valid = (tq0 + t_local) < a.nq;
+        const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16; /* this warp's quarter of the TMEM lanes */
+        const unsigned tm_o = tmem + 256u + 128u * x + lane_base;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; j++) {
+            const unsigned tm_s = tmem + 128u * x + 64u * (j & 1) + lane_base;
+            ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B3_SF + 2 * x + (j & 1)), (unsigned)(j >> 1) & 1u, s_abort, a.err, 30u));   /* keep the warp together */
+            const bool tr = (warp & 3) == 0 && lane == 0;   /* trace builds: the first warp of each tile */
+            if (tr) PF_TRACE(j, x, 0);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int k0 = j * kKeys3;
+            const bool masked = (k0 + kKeys3 - 1 > a.base + tq0);   /* the tile crosses the diagonal of some row */
+            unsigned v0[32], v1[32];
+            tmem_ld32_nowait(tm_s, v0);
+            tmem_ld32_nowait(tm_s + 32u, v1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (tr) PF_TRACE(j, x, 1);
+            if (masked) {      /* only the tiles on the diagonal pay for the causal test */
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (k0 + i > qpos) v0[i] = 0xff800000u;
+                    if (k0 + 32 + i > qpos) v1[i] = 0xff800000u;
+                }
+            }
+            /* the maximum is taken over the raw scores (the scale is positive) and the scale is folded into the exponent's
+             * argument: one FFMA per element.  Four independent chains keep the dependent-issue latency hidden. */
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 32; i++) mx4[i & 3] = fmax3(mx4[i & 3], __uint_as_float(v0[i]), __uint_as_float(v1[i]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kScaleLog2;
+            if (tr) PF_TRACE(j, x, 2);
+            /* a tile that is masked for the whole row (its keys all lie behind the row's query; only in the last tiles of
+             * the CTA) has mx = -inf: nothing moves and all its P are 0 */
+            const bool grow = mx > m + kPfThreshold;              /* true while m == -inf (key 0 is never masked) */
+            const float m_new = grow ? mx : m;
+            const float neg_m = -m_new;
+            unsigned pk[32];
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                /* the denominator sums the unrounded values: the fp16 rounding of P is a zero-mean 2^-12 relative error per
+                 * term, far below the tolerance */
+                const float e0 = ex2f(fmaf(__uint_as_float(v0[i]), kScaleLog2, neg_m)), e1 = ex2f(fmaf(__uint_as_float(v0[i + 1]), kScaleLog2, neg_m));
+                const float e2 = ex2f(fmaf(__uint_as_float(v1[i]), kScaleLog2, neg_m)), e3 = ex2f(fmaf(__uint_as_float(v1[i + 1]), kScaleLog2, neg_m));
+                pk[i >> 1] = pack_h2(e0, e1); pk[16 + (i >> 1)] = pack_h2(e2, e3);
+                ls[0] += e0; ls[1] += e1; ls[2] += e2; ls[3] += e3;
+            }
+            const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            if (tr) PF_TRACE(j, x, 3);
+            /* tcgen05.ld / .st are warp-collective: the whole warp rescales its 32 rows as soon as one of them moved its
+             * reference (the others multiply by exactly 1).  O_x is only ours when P_x(j-1).V_(j-1) has completed; it
+             * cannot be further behind than that, because S_x(j) was issued behind P_x(j-2).V_(j-2). */
+            const float alpha = grow ? ex2f(m - m_new) : 1.f;     /* 0 on the first tile (m = -inf) */
+            if (__any_sync(0xffffffffu, grow)) {
+                if (j > 0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B3_O + x), (unsigned)(j - 1) & 1u, s_abort, a.err, 31u));
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (ok) {
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            unsigned v[32];
+                            tmem_ld32(tm_o + 32u * c, v);
+#pragma unroll
+                            for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                            tmem_st32(tm_o + 32u * c, v);
+                        }
+                    }
+                }
+                l *= alpha;
+                m = m_new;
+            }
+            if (tr) PF_TRACE(j, x, 4);
+            l += lsum;
+            /* P over the first 32 columns of this S buffer (column c = keys 2c, 2c+1) */
+            tmem_st32(tm_s, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(B3_P + 2 * x + (j & 1)));
+            if (tr) PF_TRACE(j, x, 5);
+        }
+        /* epilogue: O / l.  A parity wait can only tell the last completed phase from the one before it, and all that is
+         * known here is that P.V of tile ntiles-3 has completed (S of the last tile was issued behind it): wait for the
+         * last but one first */
+        if (ok && ntiles > 1) ok = mbar_wait_blocking(BAR(B3_O + x), (unsigned)(ntiles - 2) & 1u, s_abort, a.err, 32u);
+        if (ok && ntiles > 0) ok = mbar_wait_blocking(BAR(B3_O + x), (unsigned)(ntiles - 1) & 1u, s_abort, a.err, 33u);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__all_sync(0xffffffffu, ok) && ntiles > 0) {      /* warp-uniform: tcgen05.ld is warp-collective */
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float *orow = a.out + (size_t)(tq0 + t_local) * a.out_stride + (size_t)((a.kv_head_begin + hl) * 8 + h) * HY3A_D;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                unsigned v[32];
+                tmem_ld32(tm_o + 32u * c, v);
+                if (row_valid)
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4 *>(orow + 32 * c + i) = make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
+                                                                                   __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            }
+        }
+    }
+    /* ---- common exit: everybody arrives here, also after a wait ran out; release TMEM */
+    if (*s_abort && warp == 8 && lane == 0) {
+        /* copies already issued must land before the shared memory goes away */
+        for (int st = 0; st < kSt3; st++)
+            for (unsigned ph = 0; ph < 2; ph++)
+                for (unsigned spin = 0; spin < (1u << 12) && !mbar_test(BAR(B3_KF + st), ph) && !mbar_test(BAR(B3_VF + st), ph); spin++) __nanosleep(64);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+#undef BAR
+}
+
+
 } /* namespace */
 
 typedef CUresult (*hy3a_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -797,6 +829,11 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
     }
 
     { const char *e = getenv("HY3A_PF_STOP"); if (e && atoi(e) == 1) return HY3A_OK; }   /* development: pass 1 only */
+    /* HY3A_PF_GEN=2: the second-generation kernel (128-key tiles, one S buffer per Q tile); default 3: 64-key tiles, S
+     * double-buffered */
+    int gen = 3;
+    { const char *e = getenv("HY3A_PF_GEN"); if (e && atoi(e) == 2) gen = 2; }
+    const int keys = gen == 3 ? kKeys3 : kKeys;
     CUtensorMap tq, tk, tv;
     {
         const cuuint64_t dq[3] = {HY3A_D, HY3A_N_HEAD, (cuuint64_t)nq}, sq[2] = {HY3A_D * 2, HY3A_N_HEAD * HY3A_D * 2};
@@ -804,7 +841,7 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
         int rc = make_map(ctx, &tq, const_cast<void *>(q16), dq, sq, bq);
         if (rc) return rc;
         const cuuint64_t dk[3] = {HY3A_D, (cuuint64_t)tok_stride, (cuuint64_t)kvh}, sk[2] = {HY3A_D * 2, (cuuint64_t)tok_stride * HY3A_D * 2};
-        const cuuint32_t bk[3] = {64, kKeys, 1};
+        const cuuint32_t bk[3] = {64, (cuuint32_t)keys, 1};
         rc = make_map(ctx, &tk, ws_k, dk, sk, bk);
         if (rc) return rc;
         const cuuint64_t dv[3] = {(cuuint64_t)tok_stride, HY3A_D, (cuuint64_t)kvh}, sv[2] = {(cuuint64_t)tok_stride * 2, (cuuint64_t)tok_stride * HY3A_D * 2};
@@ -815,21 +852,19 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
     static bool attr_dev[64];   /* function attributes are per device */
     bool &attr_set = attr_dev[ctx->device & 63];
     if (!attr_set) {
-        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel_v1, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
-        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPf2Smem));
+        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize, kPf2Smem));
+        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPf3Smem));
         attr_set = true;
     }
     prefill_args a;
     a.out = out; a.out_stride = out_stride; a.base = base_slot; a.nq = nq; a.kv_head_begin = ctx->cfg.kv_head_begin; a.err = ctx->d_err; a.trace = ctx->d_trace;
-    const char *v1 = getenv("HY3A_PF_V1");   /* first-generation kernel: one Q tile per CTA, P through shared memory */
-    if (v1 && atoi(v1)) {
-        dim3 g2((nq + kQTok - 1) / kQTok, kvh);
-        hy3a_prefill_kernel_v1<<<g2, kPfThreads, kPfSmem, ctx->stream>>>(tq, tk, tv, a);
-    } else {
+    {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((nq + kQTok2 - 1) / kQTok2, kvh); cfg.blockDim = dim3(kPf2Threads); cfg.dynamicSmemBytes = kPf2Smem; cfg.stream = ctx->stream;
+        cfg.gridDim = dim3((nq + kQTok2 - 1) / kQTok2, kvh); cfg.stream = ctx->stream;
+        cfg.blockDim = dim3(gen == 3 ? kPf3Threads : kPf2Threads); cfg.dynamicSmemBytes = gen == 3 ? kPf3Smem : kPf2Smem;
         cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-        HY3A_CUDA(ctx, cudaLaunchKernelEx(&cfg, hy3a_prefill_kernel, tq, tk, tv, a));
+        if (gen == 3) HY3A_CUDA(ctx, cudaLaunchKernelEx(&cfg, hy3a_prefill_kernel, tq, tk, tv, a));
+        else HY3A_CUDA(ctx, cudaLaunchKernelEx(&cfg, hy3a_prefill_kernel_v2, tq, tk, tv, a));
     }
     ctx->launches++;
     ctx->bulk_write_pending = 1;
