@@ -481,7 +481,9 @@ constexpr int kSt3 = 4;                         /* ring stages */
 constexpr int kPf3Threads = 352;
 constexpr int kOff3Q = 0, kOff3K = kOff3Q + 2 * kTileBytes, kOff3V = kOff3K + kSt3 * kK3Bytes, kOff3Bar = kOff3V + kSt3 * kK3Bytes;
 constexpr int kPf3Smem = kOff3Bar + 512 + 1024;
-enum { B3_Q = 0, B3_KF = 1, B3_KE = 5, B3_VF = 9, B3_VE = 13, B3_SF = 17, B3_P = 21, B3_O = 25 };   /* KF..VE [4 stages]; SF, P [tile][buffer]; O [tile] */
+/* K0F, K0E [2]: the first two K tiles (loaded / consumed); DF, DE [4 stages]: step j's data = V_j and K_(j+2) (loaded /
+ * consumed); SF, P [tile][buffer]; O [tile] */
+enum { B3_Q = 0, B3_K0F = 1, B3_K0E = 3, B3_DF = 5, B3_DE = 9, B3_SF = 13, B3_P = 17, B3_O = 21 };
 constexpr unsigned kIdescN64 = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 __device__ __forceinline__ void umma_f16_n64_elect(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
     asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
@@ -506,7 +508,8 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (tid == 0) {
         *s_abort = 0;
         mbar_init(BAR(B3_Q), 1);
-        for (int i = 0; i < kSt3; i++) { mbar_init(BAR(B3_KF + i), 1); mbar_init(BAR(B3_KE + i), 2); mbar_init(BAR(B3_VF + i), 1); mbar_init(BAR(B3_VE + i), 2); }   /* KE, VE: one commit per issuer */
+        for (int i = 0; i < 2; i++) { mbar_init(BAR(B3_K0F + i), 1); mbar_init(BAR(B3_K0E + i), 2); }
+        for (int i = 0; i < kSt3; i++) { mbar_init(BAR(B3_DF + i), 1); mbar_init(BAR(B3_DE + i), 2); }   /* K0E, DE: one commit per issuer */
         for (int i = 0; i < 4; i++) { mbar_init(BAR(B3_SF + i), 1); mbar_init(BAR(B3_P + i), 4); }   /* P: one arrival per softmax warp of the tile */
         mbar_init(BAR(B3_O), 1); mbar_init(BAR(B3_O + 1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -533,20 +536,24 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 tma_load_3d(sbase + kOff3Q + x * kTileBytes, &tm_q, BAR(B3_Q), 0, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
                 tma_load_3d(sbase + kOff3Q + x * kTileBytes + 16384, &tm_q, BAR(B3_Q), 64, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
             }
-            /* K runs two tiles ahead of V: S_(j+2) is issued behind P_j.V_j */
-            for (int j = 0; j < ntiles + 2; j++) {
-                if (j < ntiles) {
-                    const int st = j & (kSt3 - 1); const unsigned ph = (unsigned)(j / kSt3) & 1u;
-                    if (!mbar_wait_blocking(BAR(B3_KE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
-                    mbar_expect_tx(BAR(B3_KF + st), kK3Bytes);
-                    tma_load_3d(sbase + kOff3K + st * kK3Bytes, &tm_k, BAR(B3_KF + st), 0, j * kKeys3, hl);
-                    tma_load_3d(sbase + kOff3K + st * kK3Bytes + 8192, &tm_k, BAR(B3_KF + st), 64, j * kKeys3, hl);
-                }
-                if (j >= 2) {
-                    const int jv = j - 2, st = jv & (kSt3 - 1); const unsigned ph = (unsigned)(jv / kSt3) & 1u;
-                    if (!mbar_wait_blocking(BAR(B3_VE + st), ph ^ 1u, s_abort, a.err, 11u)) break;
-                    mbar_expect_tx(BAR(B3_VF + st), kK3Bytes);
-                    tma_load_3d(sbase + kOff3V + st * kK3Bytes, &tm_v, BAR(B3_VF + st), jv * kKeys3, 0, hl);
+            /* the first two K tiles, then per step j one transaction: V_j and K_(j+2) (S_(j+2) is issued behind P_j.V_j,
+             * so the issuers need both at the same time and wait for them once) */
+            for (int j = 0; j < 2 && j < ntiles; j++) {
+                mbar_expect_tx(BAR(B3_K0F + j), kK3Bytes);
+                tma_load_3d(sbase + kOff3K + j * kK3Bytes, &tm_k, BAR(B3_K0F + j), 0, j * kKeys3, hl);
+                tma_load_3d(sbase + kOff3K + j * kK3Bytes + 8192, &tm_k, BAR(B3_K0F + j), 64, j * kKeys3, hl);
+            }
+            for (int j = 0; j < ntiles; j++) {
+                const int st = j & (kSt3 - 1), j2 = j + 2, st2 = j2 & (kSt3 - 1); const unsigned ph = (unsigned)(j / kSt3) & 1u;
+                /* V slot st held V_(j-4), K slot st2 held K_(j-2): both were released by step j-4 -- except K_0 and K_1, which
+                 * the issuers release on barriers of their own */
+                if (!mbar_wait_blocking(BAR(B3_DE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
+                if ((j == 2 || j == 3) && j2 < ntiles && !mbar_wait_blocking(BAR(B3_K0E + j - 2), 0u, s_abort, a.err, 11u)) break;
+                mbar_expect_tx(BAR(B3_DF + st), j2 < ntiles ? 2 * kK3Bytes : kK3Bytes);
+                tma_load_3d(sbase + kOff3V + st * kK3Bytes, &tm_v, BAR(B3_DF + st), j * kKeys3, 0, hl);
+                if (j2 < ntiles) {
+                    tma_load_3d(sbase + kOff3K + st2 * kK3Bytes, &tm_k, BAR(B3_DF + st), 0, j2 * kKeys3, hl);
+                    tma_load_3d(sbase + kOff3K + st2 * kK3Bytes + 8192, &tm_k, BAR(B3_DF + st), 64, j2 * kKeys3, hl);
                 }
             }
         }
@@ -566,26 +573,23 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             for (int kk = 0; kk < 8; kk++)      /* the second half of d lies one sub-tile further on: 16 KB for Q, 8 KB for K */
                 umma_f16_n64_elect(d, dQ + (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2), k + (unsigned long long)((kk >> 2) * 512 + (kk & 3) * 2), kk > 0);
             umma_commit_elect(BAR(B3_SF + 2 * x + (j & 1)));
-            umma_commit_elect(BAR(B3_KE + (j & (kSt3 - 1))));
         };
         /* tile B starts when the first softmax of tile A is through: half a period out of phase, the MMAs of one tile
          * run while the other tile's issuer is between two steps and its softmax warps have the SM's exponential
          * unit to themselves (nothing pulls the two loops apart by itself when they start together) */
         if (ok && x == 1) ok = mbar_wait_blocking(BAR(B3_P + 0), 0u, s_abort, a.err, 22u);
         for (int j = 0; j < 2 && j < ntiles && ok; j++) {
-            ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B3_KF + j), 0u, s_abort, a.err, 21u));
+            ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B3_K0F + j), 0u, s_abort, a.err, 21u));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_qk(j);
+            umma_commit_elect(BAR(B3_K0E + j));
         }
         for (int j = 0; j < ntiles && ok; j++) {
-            const int st = j & (kSt3 - 1); const unsigned ph = (unsigned)(j / kSt3) & 1u;
-            const int j2 = j + 2, st2 = j2 & (kSt3 - 1); const unsigned ph2 = (unsigned)(j2 / kSt3) & 1u;
+            const int st = j & (kSt3 - 1), j2 = j + 2; const unsigned ph = (unsigned)(j / kSt3) & 1u;
             PF_TRACE2(j, x, 0);
-            ok = mbar_wait_blocking(BAR(B3_VF + st), ph, s_abort, a.err, 23u);
+            ok = mbar_wait_blocking(BAR(B3_DF + st), ph, s_abort, a.err, 23u);                                               /* V_j and K_(j+2) */
             PF_TRACE2(j, x, 1);
-            if (ok && j2 < ntiles) ok = mbar_wait_blocking(BAR(B3_KF + st2), ph2, s_abort, a.err, 25u);
-            PF_TRACE2(j, x, 2);
             if (ok) ok = mbar_wait_blocking(BAR(B3_P + 2 * x + (j & 1)), (unsigned)(j >> 1) & 1u, s_abort, a.err, 24u);   /* P_x(j) in tensor memory, O_x rescaled */
             PF_TRACE2(j, x, 3);
             ok = __all_sync(0xffffffffu, ok);
@@ -602,9 +606,9 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
             PF_TRACE3(j, x, 0);
             umma_commit_elect(BAR(B3_O + x));
-            umma_commit_elect(BAR(B3_VE + st));
             PF_TRACE3(j, x, 1);
             if (j2 < ntiles) issue_qk(j2);
+            umma_commit_elect(BAR(B3_DE + st));
             if (lane == 0) PF_TRACE(j, x, 7);
         }
     } else {
@@ -720,7 +724,7 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         /* copies already issued must land before the shared memory goes away */
         for (int st = 0; st < kSt3; st++)
             for (unsigned ph = 0; ph < 2; ph++)
-                for (unsigned spin = 0; spin < (1u << 12) && !mbar_test(BAR(B3_KF + st), ph) && !mbar_test(BAR(B3_VF + st), ph); spin++) __nanosleep(64);
+                for (unsigned spin = 0; spin < (1u << 12) && !mbar_test(BAR(B3_DF + st), ph); spin++) __nanosleep(64);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
