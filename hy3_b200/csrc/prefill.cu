@@ -136,9 +136,13 @@ __global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cac
     const int block = cache.block_table[(size_t)seq * cache.max_blocks_per_seq + pg];
     const uint8_t *page = cache.pool + hy3a_page_index(cache, block, layer, hl) * (size_t)cache.page_bytes;
     const __half *ks = reinterpret_cast<const __half *>(page + g.ks_off), *vs = reinterpret_cast<const __half *>(page + g.vs_off);
-    /* K: 128 tokens x 16 groups of 8 dims */
-    for (int idx = tid; idx < 128 * 16; idx += 256) {
-        const int tok = idx >> 4, d = (idx & 15) * 8, t = pg * 128 + tok;
+    /* one block converts 32 tokens of the page (blockIdx.z): short dependent chains and 4x the blocks, because a chunk only
+     * brings a handful of new pages and the attention kernel waits for this one */
+    const int tq = blockIdx.z * 32;
+    /* K: 32 tokens x 16 groups of 8 dims */
+#pragma unroll
+    for (int idx = tid; idx < 32 * 16; idx += 256) {
+        const int tok = tq + (idx >> 4), d = (idx & 15) * 8, t = pg * 128 + tok;
         uint4 o = make_uint4(0, 0, 0, 0);
         if (t < ntok) {
             if (DT == 0) {
@@ -162,13 +166,14 @@ __global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cac
         }
         *reinterpret_cast<uint4 *>(ws_k + ((size_t)hl * tok_stride + t) * HY3A_D + d) = o;
     }
-    /* V^T: thread = (dim, half of the page's tokens); 8 consecutive tokens per 16-byte store */
+    /* V^T: thread = (dim, 16 of the block's tokens); 8 consecutive tokens per 16-byte store */
     const int d = tid & 127, th = tid >> 7;
-    for (int t8 = 0; t8 < 8; t8++) {
+#pragma unroll
+    for (int t8 = 0; t8 < 2; t8++) {
         __half hv[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const int tok = th * 64 + t8 * 8 + i, t = pg * 128 + tok;
+            const int tok = tq + th * 16 + t8 * 8 + i, t = pg * 128 + tok;
             float v = 0.f;
             if (t < ntok) {
                 if (DT == 0) {
@@ -185,7 +190,7 @@ __global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cac
             }
             hv[i] = __float2half_rn(v);
         }
-        *reinterpret_cast<uint4 *>(ws_vt + ((size_t)hl * HY3A_D + d) * tok_stride + pg * 128 + th * 64 + t8 * 8) = *reinterpret_cast<uint4 *>(hv);
+        *reinterpret_cast<uint4 *>(ws_vt + ((size_t)hl * HY3A_D + d) * tok_stride + pg * 128 + tq + th * 16 + t8 * 8) = *reinterpret_cast<uint4 *>(hv);
     }
 }
 
@@ -818,7 +823,7 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     if (pages > pg0) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(pages - pg0, kvh); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = ctx->stream;
+        cfg.gridDim = dim3(pages - pg0, kvh, 4); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = ctx->stream;
         cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
         __half *wk = (__half *)ws_k, *wv = (__half *)ws_v;
         cudaError_t e;
