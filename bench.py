@@ -236,7 +236,7 @@ def prefill_section(torch, dev, kv="fp16", prompt=8192, chunk=512):
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
             ctx.batch_set([0] * chunk, list(range(b, b + chunk)))
             ev[0].record()
-            ctx.append(0, q[b:b + chunk], k[b:b + chunk], v[b:b + chunk], q_out16=q16)
+            ctx.append(0, q[b:b + chunk], k[b:b + chunk], v[b:b + chunk], q_out=False, q_out16=q16)
             ev[1].record()
             ctx.prefill(0, 0, b, q16, out=out)
             ev[2].record()

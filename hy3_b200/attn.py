@@ -122,19 +122,23 @@ class Hy3Attn:
 
     # ---- hot path
     def append(self, layer, q, k, v, q_out=None, q_out16=None):
-        """q [n,64,128] / k,v [n,8,128] fp32 (row stride free, rows dense).  Returns q_out (fp32)."""
+        """q [n,64,128] / k,v [n,8,128] fp32 (row stride free, rows dense).  Returns q_out (fp32); q_out=False with a
+        q_out16 buffer writes the 16-bit queries only (the chunked prefill reads nothing else)."""
         import torch
         n = self.batch_n
         assert (k is None) == (v is None)
         for t in (q, k, v):
             assert t is None or (t.shape[0] == n and t.dtype == torch.float32 and t.stride(-1) == 1 and t.stride(-2) == D)
-        if q_out is None:
+        if q_out is False:
+            assert q_out16 is not None
+            q_out = None
+        elif q_out is None:
             q_out = torch.empty((n, H, D), dtype=torch.float32, device=q.device)
         if q_out16 is not None:
             assert q_out16.dtype == torch.float16 and q_out16.is_contiguous() and q_out16.numel() == n * H * D
         self._chk(self.lib.hy3a_append(self.h, layer, _ptr(q), q.stride(0), _ptr(k), 0 if k is None else k.stride(0),
                                        _ptr(v), 0 if v is None else v.stride(0),
-                                       _ptr(q_out), q_out.stride(0), _ptr(q_out16)))
+                                       _ptr(q_out), 0 if q_out is None else q_out.stride(0), _ptr(q_out16)))
         return q_out
 
     def decode(self, layer, q, out=None, partials=None):

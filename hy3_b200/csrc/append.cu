@@ -49,11 +49,22 @@ __global__ void __launch_bounds__(256) hy3a_append_kernel(hy3a_cache_view cache,
     const int row = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hr = blockIdx.x * 8 + warp;
+    /* the RoPE coefficients depend on the row only: 64 threads compute them once for the block's 8 heads (full-range
+     * cosf/sinf are most of this kernel's instructions when every warp computes its own) */
+    __shared__ float s_cos[64], s_sin[64];
+    if (row < batch.n && blockIdx.x < 9 && threadIdx.x < 64) {
+        const int ti = batch.pos[row];
+        const int pos = (ti + (ti >= rope.pos_jump_at ? rope.pos_jump : 0)) * rope.pos_stride;
+        const float fr = (float)pos * rope.inv_freq[threadIdx.x];
+        s_cos[threadIdx.x] = cosf(fr) * rope.attn_factor;
+        s_sin[threadIdx.x] = sinf(fr) * rope.attn_factor;
+    }
+    __syncthreads();
     if (row >= batch.n || hr >= 80) return;
     const hy3a_geom g = hy3a_make_geom(DT);
     const int half = lane >> 4, idx = lane & 15;
     const int d0 = half * 64 + idx * 4;
-    const int seq = batch.seq[row], slot = batch.slot[row], ti = batch.pos[row];
+    const int seq = batch.seq[row], slot = batch.slot[row];
 
     const bool is_q = hr < 64, is_k = (hr >= 64 && hr < 72);
     const int head = is_q ? hr : (is_k ? hr - 64 : hr - 72);
@@ -63,7 +74,11 @@ __global__ void __launch_bounds__(256) hy3a_append_kernel(hy3a_cache_view cache,
     float4 xv = *reinterpret_cast<const float4 *>(src + (size_t)head * HY3A_D + d0);
     float y[4] = {xv.x, xv.y, xv.z, xv.w};
 
-    if (is_q || is_k) norm_rope_row(y, a.norm_w + (is_k ? HY3A_D : 0), a.eps, rope, ti, lane);
+    if (is_q || is_k) {
+        const float4 cv4 = *reinterpret_cast<const float4 *>(s_cos + idx * 4), sv4 = *reinterpret_cast<const float4 *>(s_sin + idx * 4);
+        const float c[4] = {cv4.x, cv4.y, cv4.z, cv4.w}, sn[4] = {sv4.x, sv4.y, sv4.z, sv4.w};
+        norm_rope_apply(y, *reinterpret_cast<const float4 *>(a.norm_w + (is_k ? HY3A_D : 0) + d0), a.eps, c, sn, lane);
+    }
     if (is_q) {
         if (a.q_out) *reinterpret_cast<float4 *>(a.q_out + (size_t)row * a.q_out_stride + (size_t)head * HY3A_D + d0) = make_float4(y[0], y[1], y[2], y[3]);
         if (a.q_out16) {

@@ -120,9 +120,9 @@ int hy3a_batch_set(hy3a_ctx *ctx, int n, const int *seq_ids, const int *slots, c
  * (hy3_gpu.cu:144, :250, :329) and their per-token launch loop (:823-829).
  * q_in/k_in/v_in: fp32 rows with the given row strides (floats) -- the reference keeps
  * them inside one 10240-float QKV row (hy3_gpu.cu:748).  q_out: normalised + rotated
- * queries, fp32 [n][64][128] with row stride q_out_stride (may alias q_in); q_out16
- * (optional, may be NULL): the same values as IEEE fp16 [n][64][128] dense, the operand
- * format of hy3a_prefill.  k_in and v_in may both be NULL: only the queries are
+ * queries, fp32 [n][64][128] with row stride q_out_stride (may alias q_in; may be NULL
+ * when only q_out16 is wanted, as in a prefill chunk); q_out16 (optional, may be NULL):
+ * the same values as IEEE fp16 [n][64][128] dense, the operand format of hy3a_prefill.  k_in and v_in may both be NULL: only the queries are
  * normalised and rotated and nothing is stored (a rank that does not own the tail of a
  * sequence-sharded cache still needs the rotated query).                               */
 int hy3a_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_stride, const float *k_in, size_t k_stride,

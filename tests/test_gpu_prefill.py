@@ -80,7 +80,7 @@ def _chunked(cuda, oracle, dt, chunks, mirror_mb, monkeypatch, redo=None):
         ctx.batch_set([0] * n, list(range(base, base + n)))
         q16 = torch.empty((n, 64, 128), dtype=torch.float16, device=cuda)
         src = slice(base + shift, base + shift + n)
-        ctx.append(1, tq[src], tk[src], tv[src], q_out16=q16)
+        ctx.append(1, tq[src], tk[src], tv[src], q_out=False, q_out16=q16)
         out = ctx.prefill(1, 0, base, q16)
         ctx.sync()
         outs.append((base, n, q16.float().cpu().numpy(), out.cpu().numpy()))
