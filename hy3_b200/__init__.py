@@ -8,3 +8,4 @@ can be inspected), but creating a context without the library or without a B200 
 """
 from ._lib import LIB_PATH, load_library, Hy3AttnError  # noqa: F401
 from .attn import Hy3Attn, KV_DTYPES, H, G, D, PAGE_TOKENS, PARTIAL_FLOATS  # noqa: F401
+from .session import EvalSession, plan_eval  # noqa: F401

@@ -50,3 +50,17 @@ def test_piece_count_formula_matches_ranges():
             u = int(u)
             owner = -(-((u + 1) * C) // U) - 1
             assert starts[owner] <= u < starts[owner + 1]
+
+
+def test_plan_eval_follows_the_reference_walk():
+    """hy3_gpu.cu:857-889: with a chunk size and more than one token, all tokens but the last go through chunks; the
+    position of the first token is cache_len / n_layers."""
+    from hy3_b200.session import plan_eval, read_env
+    assert plan_eval(0, 3, 80, 0) == [("token", 0), ("token", 1), ("token", 2)]
+    assert plan_eval(160, 1300, 80, 512) == [("chunk", 2, 512), ("chunk", 514, 512), ("chunk", 1026, 275), ("token", 1301)]
+    assert plan_eval(80, 1, 80, 512) == [("token", 1)]                     # a single token never takes the chunk path
+    assert plan_eval(0, 2, 80, 512) == [("chunk", 0, 1), ("token", 1)]
+    assert plan_eval(0, 513, 2, 512) == [("chunk", 0, 512), ("token", 512)]
+    e = read_env({"HY3_KV_INT4": "1", "HY3_PREFILL_CHUNK": "abc", "HY3_POS_STRIDE": "-3", "HY3_POS_JUMP": "7"})
+    assert e == {"kv_dtype": "int4", "chunk": 0, "pos_stride": 1, "pos_jump": 7, "pos_jump_at": 0}
+    assert read_env({})["kv_dtype"] == "int8" and read_env({"HY3_KV_FP16": "1"})["kv_dtype"] == "fp16"
