@@ -37,6 +37,10 @@ struct append_args {
     const float *norm_w; /* [2][128] for this layer */
     float eps;
     int layer;
+    /* write-through into the layer's fp16 prefill operands (NULL = none): K rows [head][token][128] and V transposed
+     * [head][128][mirror_stride], the values the conversion kernel of the chunked prefill would produce */
+    __half *mirror_k, *mirror_v;
+    int mirror_stride;
 };
 
 /* grid (10, n_rows), block 256: warp (blockIdx.x*8 + warp) in [0,80) = 64 Q, 8 K, 8 V heads. */
@@ -92,8 +96,124 @@ __global__ void __launch_bounds__(256) hy3a_append_kernel(hy3a_cache_view cache,
     }
     const int hl = head - cache.kv_head_begin;
     uint8_t *page = page_ptr(cache, seq, slot, a.layer, hl);
-    unsigned sb = store_row<DT>(page, g, slot & 127, !is_k, y, d0, lane);
+    int codes[4];
+    unsigned sb = store_row<DT>(page, g, slot & 127, !is_k, y, d0, lane, nullptr, codes);
     if (DT != 0 && !is_k && lane == 0) atomicMax(cache.vs_max + a.layer * cache.kv_heads + hl, sb);
+    if (a.mirror_k) {
+        /* value = code * stored fp16 scale (hy3_gpu.cu:206-215), or the fp16 value itself; rounded to fp16 */
+        __half hv[4];
+        const float sc = DT == 0 ? 0.f : __half2float(__ushort_as_half((unsigned short)sb));
+#pragma unroll
+        for (int j = 0; j < 4; j++) hv[j] = DT == 0 ? __float2half_rn(y[j]) : __float2half_rn((float)codes[j] * sc);
+        if (is_k) {
+            *reinterpret_cast<uint2 *>(a.mirror_k + ((size_t)hl * a.mirror_stride + slot) * HY3A_D + d0) = *reinterpret_cast<uint2 *>(hv);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) a.mirror_v[((size_t)hl * HY3A_D + d0 + j) * a.mirror_stride + slot] = hv[j];
+        }
+    }
+}
+
+/* ---- the same work for a chunk of rows (prefill): blocks shaped for throughput -----------------------------------
+ * With hundreds of rows the per-row blocks above are bound by their own latency (5 120 blocks for 512 rows, each with a
+ * cosf/sinf stage in front of one 512-byte load per warp).  Here all blocks of a chunk are resident at once:
+ *   blocks [0, n)            one row each: the 64 query heads, 8 per warp, loads issued up front, RoPE coefficients once
+ *                            per row;
+ *   blocks [n, n + kvh*ng)   one owned KV head x 8 consecutive rows (ng = ceil(n / 8)), warp = row: K and V of that head.
+ *                            Eight consecutive tokens of one head in one block make the write-through of the
+ *                            TRANSPOSED V operand a 16-byte store per head dim (staged in shared memory).
+ * The arithmetic is the per-row kernel's (same rowops functions), so codes, scales and queries are identical bits. */
+template <int DT>
+__global__ void __launch_bounds__(256) hy3a_append_chunk_kernel(hy3a_cache_view cache, hy3a_batch_view batch, hy3a_rope_params rope, append_args a, int aligned8) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = batch.n;
+    const int half = lane >> 4, idx = lane & 15, d0 = half * 64 + idx * 4;
+    const hy3a_geom g = hy3a_make_geom(DT);
+    if ((int)blockIdx.x < n) {
+        /* ---- query block */
+        const int row = blockIdx.x;
+        __shared__ float s_cos[64], s_sin[64];
+        if (threadIdx.x < 64) {
+            const int ti = batch.pos[row];
+            const int pos = (ti + (ti >= rope.pos_jump_at ? rope.pos_jump : 0)) * rope.pos_stride;
+            const float fr = (float)pos * rope.inv_freq[threadIdx.x];
+            s_cos[threadIdx.x] = cosf(fr) * rope.attn_factor;
+            s_sin[threadIdx.x] = sinf(fr) * rope.attn_factor;
+        }
+        float4 xv[8];
+        const float *src = a.q_in + (size_t)row * a.q_stride + d0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) xv[i] = *reinterpret_cast<const float4 *>(src + (size_t)(warp + 8 * i) * HY3A_D);
+        const float4 wv = *reinterpret_cast<const float4 *>(a.norm_w + d0);
+        __syncthreads();
+        const float4 cv4 = *reinterpret_cast<const float4 *>(s_cos + idx * 4), sv4 = *reinterpret_cast<const float4 *>(s_sin + idx * 4);
+        const float c[4] = {cv4.x, cv4.y, cv4.z, cv4.w}, sn[4] = {sv4.x, sv4.y, sv4.z, sv4.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int head = warp + 8 * i;
+            float y[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+            norm_rope_apply(y, wv, a.eps, c, sn, lane);
+            if (a.q_out) *reinterpret_cast<float4 *>(a.q_out + (size_t)row * a.q_out_stride + (size_t)head * HY3A_D + d0) = make_float4(y[0], y[1], y[2], y[3]);
+            if (a.q_out16) {
+                __half2 h01 = __floats2half2_rn(y[0], y[1]), h23 = __floats2half2_rn(y[2], y[3]);
+                uint2 w2;
+                w2.x = *reinterpret_cast<unsigned *>(&h01);
+                w2.y = *reinterpret_cast<unsigned *>(&h23);
+                *reinterpret_cast<uint2 *>(a.q_out16 + ((size_t)row * 64 + head) * HY3A_D + d0) = w2;
+            }
+        }
+        return;
+    }
+    /* ---- K/V block: owned head hl, rows 8 grp .. 8 grp + 7 (warp = row) */
+    const int kb = blockIdx.x - n, hl = kb % cache.kv_heads, grp = kb / cache.kv_heads;
+    const int head = cache.kv_head_begin + hl, row = grp * 8 + warp;
+    const bool live = row < n;
+    __shared__ __align__(16) __half s_vt[HY3A_D][8];
+    int slot = 0;
+    if (live) {
+        const int seq = batch.seq[row], ti = batch.pos[row];
+        slot = batch.slot[row];
+        const float4 kx = *reinterpret_cast<const float4 *>(a.k_in + (size_t)row * a.k_stride + (size_t)head * HY3A_D + d0);
+        const float4 vx = *reinterpret_cast<const float4 *>(a.v_in + (size_t)row * a.v_stride + (size_t)head * HY3A_D + d0);
+        uint8_t *page = page_ptr(cache, seq, slot, a.layer, hl);
+        int codes[4];
+        {
+            float y[4] = {kx.x, kx.y, kx.z, kx.w};
+            norm_rope_row(y, a.norm_w + HY3A_D, a.eps, rope, ti, lane);
+            const unsigned sb = store_row<DT>(page, g, slot & 127, false, y, d0, lane, nullptr, codes);
+            if (a.mirror_k) {
+                __half hv[4];
+                const float sc = DT == 0 ? 0.f : __half2float(__ushort_as_half((unsigned short)sb));
+#pragma unroll
+                for (int j = 0; j < 4; j++) hv[j] = DT == 0 ? __float2half_rn(y[j]) : __float2half_rn((float)codes[j] * sc);
+                *reinterpret_cast<uint2 *>(a.mirror_k + ((size_t)hl * a.mirror_stride + slot) * HY3A_D + d0) = *reinterpret_cast<uint2 *>(hv);
+            }
+        }
+        {
+            float y[4] = {vx.x, vx.y, vx.z, vx.w};
+            const unsigned sb = store_row<DT>(page, g, slot & 127, true, y, d0, lane, nullptr, codes);
+            if (DT != 0 && lane == 0) atomicMax(cache.vs_max + a.layer * cache.kv_heads + hl, sb);
+            if (a.mirror_k) {
+                const float sc = DT == 0 ? 0.f : __half2float(__ushort_as_half((unsigned short)sb));
+#pragma unroll
+                for (int j = 0; j < 4; j++) s_vt[d0 + j][warp] = DT == 0 ? __float2half_rn(y[j]) : __float2half_rn((float)codes[j] * sc);
+            }
+        }
+    }
+    if (!a.mirror_k) return;      /* uniform over the block */
+    __syncthreads();
+    if (threadIdx.x < HY3A_D) {
+        /* rows of a mirrored chunk are consecutive slots of one sequence: the block's 8 tokens are 8 adjacent columns */
+        const int d = threadIdx.x, slot_base = batch.slot[grp * 8];
+        __half *dst = a.mirror_v + ((size_t)hl * HY3A_D + d) * a.mirror_stride + slot_base;
+        const int nrow = min(8, n - grp * 8);
+        if (aligned8 && nrow == 8) {
+            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(&s_vt[d][0]);
+        } else {
+            for (int t = 0; t < nrow; t++) dst[t] = s_vt[d][t];
+        }
+    }
 }
 
 /* ---- device-side seeded fill (benchmark set-up) ----------------------------------- */
@@ -209,6 +329,14 @@ int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_str
     a.q_in = q_in; a.k_in = k_in; a.v_in = v_in; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
     a.q_out = q_out; a.q_out_stride = q_out_stride; a.q_out16 = (__half *)q_out16;
     a.norm_w = ctx->d_norm_w + (size_t)layer * 2 * HY3A_D; a.eps = ctx->cfg.rms_eps; a.layer = layer;
+    /* rows that extend the sequence whose prefill operands this layer keeps, gap-free: convert them here, where they are
+     * in registers, instead of reading the pages back in the conversion kernel */
+    a.mirror_k = a.mirror_v = NULL; a.mirror_stride = 0;
+    if (k_in && ctx->pf_mk[layer] && ctx->batch_contig && ctx->batch_seq0 == ctx->pf_mseq && ctx->batch_slot0 == ctx->pf_mntok[layer] &&
+        ctx->batch_slot0 + ctx->batch_n <= ctx->pf_mcap[layer]) {
+        a.mirror_k = (__half *)ctx->pf_mk[layer]; a.mirror_v = (__half *)ctx->pf_mv[layer]; a.mirror_stride = ctx->pf_mcap[layer];
+        ctx->pf_mntok[layer] = ctx->batch_slot0 + ctx->batch_n;
+    }
     hy3a_cache_view cv = hy3a_view(ctx);
     hy3a_batch_view bv = hy3a_bview(ctx);
     cudaLaunchConfig_t cfg = {};
@@ -218,6 +346,21 @@ int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_str
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
     cudaError_t e;
+    if (ctx->batch_n >= 32) {      /* a chunk: the throughput-shaped kernel */
+        const int n = ctx->batch_n, kv_blocks = k_in ? ctx->cfg.kv_head_count * ((n + 7) / 8) : 0;
+        const int aligned8 = a.mirror_k && (ctx->batch_slot0 % 8 == 0) && (ctx->pf_mcap[layer] % 8 == 0);
+        cfg.gridDim = dim3(n + kv_blocks);
+        switch (ctx->geom.dtype) {
+            case 0: e = cudaLaunchKernelEx(&cfg, hy3a_append_chunk_kernel<0>, cv, bv, ctx->rope, a, aligned8); break;
+            case 1: e = cudaLaunchKernelEx(&cfg, hy3a_append_chunk_kernel<1>, cv, bv, ctx->rope, a, aligned8); break;
+            case 3: e = cudaLaunchKernelEx(&cfg, hy3a_append_chunk_kernel<3>, cv, bv, ctx->rope, a, aligned8); break;
+            default: e = cudaLaunchKernelEx(&cfg, hy3a_append_chunk_kernel<2>, cv, bv, ctx->rope, a, aligned8); break;
+        }
+        ctx->launches++;
+        ctx->bulk_write_pending = 1;
+        HY3A_CUDA(ctx, e);
+        return HY3A_OK;
+    }
     switch (ctx->geom.dtype) {
         case 0: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<0>, cv, bv, ctx->rope, a); break;
         case 1: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<1>, cv, bv, ctx->rope, a); break;

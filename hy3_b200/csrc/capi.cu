@@ -363,6 +363,8 @@ int hy3a_batch_set(hy3a_ctx *ctx, int n, const int *seq_ids, const int *slots, c
     free(tmp);
     if (rc) return rc;
     ctx->batch_n = n;
+    ctx->batch_seq0 = seq_ids[0]; ctx->batch_slot0 = slots[0]; ctx->batch_contig = slots[0] >= 0;
+    for (int i = 1; i < n && ctx->batch_contig; i++) ctx->batch_contig = seq_ids[i] == seq_ids[0] && slots[i] == slots[0] + i;
     return HY3A_OK;
 }
 

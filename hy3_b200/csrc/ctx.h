@@ -89,6 +89,7 @@ struct hy3a_ctx {
     int ring_next;
     unsigned int *h_err;  /* pinned */
     int batch_n;
+    int batch_contig, batch_seq0, batch_slot0;   /* the batch is rows slot0, slot0+1, ... of one sequence (a prefill chunk) */
     int decode_ctas;
     int bulk_write_pending; /* a kernel that wrote many KV slots was enqueued and no decode launch has followed it yet */
     int use_pdl;          /* launch kernels with programmatic stream serialization (HY3A_NO_PDL=1 turns it off) */

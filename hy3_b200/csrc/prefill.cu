@@ -786,7 +786,10 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
                 HY3A_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
                 cudaFree(ctx->pf_mk[layer]); cudaFree(ctx->pf_mv[layer]);
                 ctx->pf_mk[layer] = ctx->pf_mv[layer] = NULL; ctx->pf_mcap[layer] = 0; ctx->pf_mntok[layer] = 0; ctx->pf_mbytes -= old_b;
-                if (cudaMalloc(&ctx->pf_mk[layer], new_b / 2) == cudaSuccess && cudaMalloc(&ctx->pf_mv[layer], new_b / 2) == cudaSuccess) {
+                /* zeroed once: columns past a sequence's end are read by the last tile (and masked), so they must never
+                 * hold a NaN or Inf pattern; afterwards only finite values are written */
+                if (cudaMalloc(&ctx->pf_mk[layer], new_b / 2) == cudaSuccess && cudaMalloc(&ctx->pf_mv[layer], new_b / 2) == cudaSuccess &&
+                    cudaMemsetAsync(ctx->pf_mk[layer], 0, new_b / 2, ctx->stream) == cudaSuccess && cudaMemsetAsync(ctx->pf_mv[layer], 0, new_b / 2, ctx->stream) == cudaSuccess) {
                     ctx->pf_mcap[layer] = cap; ctx->pf_mbytes += new_b;
                 } else {
                     cudaGetLastError();
@@ -797,7 +800,8 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
         if (want <= ctx->pf_mcap[layer]) {
             ws_k = ctx->pf_mk[layer]; ws_v = ctx->pf_mv[layer];
             tok_stride = ctx->pf_mcap[layer];
-            pg0 = ctx->pf_mntok[layer] / HY3A_PT;          /* a partly filled page is converted again */
+            /* a partly filled page is converted again; nothing is, when the append kernel wrote the rows through */
+            pg0 = ctx->pf_mntok[layer] >= ntok ? pages : ctx->pf_mntok[layer] / HY3A_PT;
             if (ctx->pf_mntok[layer] < ntok) ctx->pf_mntok[layer] = ntok;
         }
     }

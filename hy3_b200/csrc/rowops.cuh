@@ -27,7 +27,8 @@ __device__ __forceinline__ uint8_t *page_ptr(const hy3a_cache_view &c, int seq, 
  * Returns the fp16 scale bits (0 for FP16 caches).                                    */
 template <int DT>
 __device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g, int tok, bool is_v, const float y[4], int d0, int lane,
-                                              uint8_t *scale_page = nullptr /* where the scale goes, if not into `page` (a shared-memory copy split in two) */) {
+                                              uint8_t *scale_page = nullptr /* where the scale goes, if not into `page` (a shared-memory copy split in two) */,
+                                              int *codes_out = nullptr /* the lane's 4 codes (quantised caches) */) {
     if (DT == 0) {
         __half2 h01 = __floats2half2_rn(y[0], y[1]);
         __half2 h23 = __floats2half2_rn(y[2], y[3]);
@@ -47,6 +48,7 @@ __device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g,
     int c[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) c[j] = (int)roundf(fmaxf(-qmax, fminf(qmax, __fmul_rn(y[j], inv))));
+    if (codes_out) { codes_out[0] = c[0]; codes_out[1] = c[1]; codes_out[2] = c[2]; codes_out[3] = c[3]; }
     __half sh = __float2half(s);
     unsigned sbits = (unsigned)__half_as_ushort(sh);
     if (lane == 0) *reinterpret_cast<unsigned short *>((scale_page ? scale_page : page) + (is_v ? g.vs_off : g.ks_off) + tok * 2) = (unsigned short)sbits;

@@ -129,3 +129,35 @@ def test_committed_gpu_fixture(cuda, oracle):
         assert np.array_equal(vs, g["vslots_" + dt])
         assert np.array_equal(make_slots(oracle, v, dt), g["vslots_" + dt])
         assert np.array_equal(make_slots(oracle, k, dt), g["kslots_" + dt])
+
+
+@pytest.mark.parametrize("dt", ["int8", "int4", "fp16"])
+def test_chunk_kernel_equals_row_kernel(cuda, oracle, dt):
+    """Batches of 32 rows or more take the throughput-shaped kernel (one block per row for the queries, one block per KV
+    head and 8 rows for K/V); smaller ones the per-row kernel.  Same rows, same slots and positions: identical cache
+    bytes and identical fp32 / fp16 queries."""
+    import torch
+    from hy3_b200 import Hy3Attn
+    n, slot0 = 197, 3                         # not a multiple of 8, not aligned: the ragged last K/V block is covered
+    q = oracle.fill_normal((n, 64, 128), SEED, 801)
+    k = oracle.fill_normal((n, 8, 128), SEED, 802)
+    v = oracle.fill_normal((n, 8, 128), SEED, 803)
+    w = (1.0 + 0.02 * oracle.fill_normal((2, 128), SEED, 3)).astype(np.float32)
+    pos = [slot0 + i + (1000 if i > 100 else 0) for i in range(n)]     # RoPE positions need not be the slots
+    tq, tk, tv = (torch.from_numpy(a).to(cuda) for a in (q, k, v))
+    res = []
+    for step in (n, 16):
+        ctx = Hy3Attn(kv_dtype=dt, n_layers=1, max_batch=n, max_tokens=512)
+        ctx.set_norm_weights(0, w[0], w[1])
+        qo = torch.empty((n, 64, 128), device=cuda)
+        q16 = torch.empty((n, 64, 128), dtype=torch.float16, device=cuda)
+        for b in range(0, n, step):
+            e = min(n, b + step)
+            ctx.batch_set([0] * (e - b), list(range(slot0 + b, slot0 + e)), pos[b:e])
+            ctx.append(0, tq[b:e], tk[b:e], tv[b:e], q_out=qo[b:e], q_out16=q16[b:e])
+        ctx.sync()
+        ks, vs = ctx.export_kv(0, 0, slot0, n)
+        res.append((qo.cpu().numpy(), q16.cpu().numpy(), ks, vs))
+        ctx.close()
+    for a, b, what in zip(res[0], res[1], ("q fp32", "q fp16", "K slots", "V slots")):
+        assert np.array_equal(a, b), what
