@@ -487,7 +487,7 @@ constexpr int kPf3Threads = 352;
 constexpr int kOff3Q = 0, kOff3K = kOff3Q + 2 * kTileBytes, kOff3V = kOff3K + kSt3 * kK3Bytes, kOff3Bar = kOff3V + kSt3 * kK3Bytes;
 constexpr int kPf3Smem = kOff3Bar + 512 + 1024;
 /* K0F, K0E [2]: the first two K tiles (loaded / consumed); DF, DE [4 stages]: step j's data = V_j and K_(j+2) (loaded /
- * consumed); SF, P [tile][buffer]; O [tile] */
+ * consumed); SF, P [tile][buffer]; O [tile][last but one, last]: each completes once */
 enum { B3_Q = 0, B3_K0F = 1, B3_K0E = 3, B3_DF = 5, B3_DE = 9, B3_SF = 13, B3_P = 17, B3_O = 21 };
 constexpr unsigned kIdescN64 = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 __device__ __forceinline__ void umma_f16_n64_elect(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
@@ -516,7 +516,7 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int i = 0; i < 2; i++) { mbar_init(BAR(B3_K0F + i), 1); mbar_init(BAR(B3_K0E + i), 2); }
         for (int i = 0; i < kSt3; i++) { mbar_init(BAR(B3_DF + i), 1); mbar_init(BAR(B3_DE + i), 2); }   /* K0E, DE: one commit per issuer */
         for (int i = 0; i < 4; i++) { mbar_init(BAR(B3_SF + i), 1); mbar_init(BAR(B3_P + i), 4); }   /* P: one arrival per softmax warp of the tile */
-        mbar_init(BAR(B3_O), 1); mbar_init(BAR(B3_O + 1), 1);
+        for (int i = 0; i < 4; i++) mbar_init(BAR(B3_O + i), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {   /* one warp allocates all 512 TMEM columns (1 CTA per SM) */
@@ -610,7 +610,9 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 for (int kk = 0; kk < 4; kk++) umma_f16_ta_elect(tm_ox, pa + 8u * kk, v + (unsigned long long)(kk * 2), kk > 0 ? 1u : acc0);
             }
             PF_TRACE3(j, x, 0);
-            umma_commit_elect(BAR(B3_O + x));
+            /* completion of P.V is only asked for directly at the end (last rescale, epilogue); before that the softmax
+             * warps learn it from S_x(j+2), which this thread issues behind it */
+            if (j + 2 >= ntiles) umma_commit_elect(BAR(B3_O + 2 * x + (j + 1 == ntiles ? 1 : 0)));
             PF_TRACE3(j, x, 1);
             if (j2 < ntiles) issue_qk(j2);
             umma_commit_elect(BAR(B3_DE + st));
@@ -672,12 +674,13 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
             if (tr) PF_TRACE(j, x, 3);
             /* tcgen05.ld / .st are warp-collective: the whole warp rescales its 32 rows as soon as one of them moved its
-             * reference (the others multiply by exactly 1).  O_x is only ours when P_x(j-1).V_(j-1) has completed; it
-             * cannot be further behind than that, because S_x(j) was issued behind P_x(j-2).V_(j-2). */
+             * reference (the others multiply by exactly 1).  O_x is only ours when P_x(j-1).V_(j-1) has completed. */
             const float alpha = grow ? ex2f(m - m_new) : 1.f;     /* 0 on the first tile (m = -inf) */
             if (__any_sync(0xffffffffu, grow)) {
                 if (j > 0) {
-                    ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B3_O + x), (unsigned)(j - 1) & 1u, s_abort, a.err, 31u));
+                    /* S_x(j+1) was issued behind P_x(j-1).V, and a commit covers everything its thread issued before */
+                    ok = __all_sync(0xffffffffu, j + 1 < ntiles ? mbar_wait_blocking(BAR(B3_SF + 2 * x + ((j + 1) & 1)), (unsigned)((j + 1) >> 1) & 1u, s_abort, a.err, 31u)
+                                                               : mbar_wait_blocking(BAR(B3_O + 2 * x), 0u, s_abort, a.err, 31u));
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     if (ok) {
 #pragma unroll
@@ -703,11 +706,10 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (lane == 0) mbar_arrive(BAR(B3_P + 2 * x + (j & 1)));
             if (tr) PF_TRACE(j, x, 5);
         }
-        /* epilogue: O / l.  A parity wait can only tell the last completed phase from the one before it, and all that is
-         * known here is that P.V of tile ntiles-3 has completed (S of the last tile was issued behind it): wait for the
-         * last but one first */
-        if (ok && ntiles > 1) ok = mbar_wait_blocking(BAR(B3_O + x), (unsigned)(ntiles - 2) & 1u, s_abort, a.err, 32u);
-        if (ok && ntiles > 0) ok = mbar_wait_blocking(BAR(B3_O + x), (unsigned)(ntiles - 1) & 1u, s_abort, a.err, 33u);
+        /* epilogue: O / l.  The issuer commits P.V of the last two tiles on barriers of their own, which therefore complete
+         * exactly once (a parity wait on a barrier that runs through many phases can only tell the last completed phase
+         * from the one before it, and a waiter here could be two behind).  The last commit covers all earlier MMAs. */
+        if (ok && ntiles > 0) ok = mbar_wait_blocking(BAR(B3_O + 2 * x + 1), 0u, s_abort, a.err, 32u);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (__all_sync(0xffffffffu, ok) && ntiles > 0) {      /* warp-uniform: tcgen05.ld is warp-collective */
             const float inv = l > 0.f ? 1.f / l : 0.f;
