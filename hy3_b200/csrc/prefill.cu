@@ -121,6 +121,19 @@ __device__ __forceinline__ void umma_f16_ta_elect(unsigned d_tmem, unsigned a_tm
 __device__ __forceinline__ void umma_commit_elect(unsigned bar) {
     asm volatile("{\n .reg .pred e;\n elect.sync _|e, 0xffffffff;\n @e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}" ::"r"(bar) : "memory");
 }
+/* the same with the election hoisted: `lead` is 1 in the lane a single elect.sync chose for the whole loop */
+__device__ __forceinline__ unsigned elect_one() {
+    unsigned p;
+    asm volatile("{\n .reg .pred e;\n elect.sync _|e, 0xffffffff;\n selp.u32 %0, 1, 0, e;\n}" : "=r"(p));
+    return p;
+}
+__device__ __forceinline__ void umma_f16_ta_lead(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned accumulate, unsigned lead) {
+    asm volatile("{\n .reg .pred p, e;\n setp.ne.b32 e, %5, 0;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate), "r"(lead) : "memory");
+}
+__device__ __forceinline__ void umma_commit_lead(unsigned bar, unsigned lead) {
+    asm volatile("{\n .reg .pred e;\n setp.ne.b32 e, %1, 0;\n @e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}" ::"r"(bar), "r"(lead) : "memory");
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) { float r; asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c)); return r; }
 __device__ __forceinline__ float ex2f(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __forceinline__ unsigned pack_h2(float lo, float hi) { unsigned r; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
@@ -478,7 +491,7 @@ hy3a_prefill_kernel_v2(const __grid_constant__ CUtensorMap tm_q, const __grid_co
  * per step, no exchange between threads) and an MMA chain that only meet at the P and S barriers.  The softmax warps
  * wait for P.V only when a row's reference maximum moved (lazy rescale of O) and at the end.
  * Warps 0-3 / 4-7: softmax of tile A / B; warp 8: TMA producer (4-stage rings of 16 KB K and V tiles); warps 9 / 10:
- * MMA issuers of tile A / B, each in uniform control flow with one elected lane (one thread issues an MMA every
+ * MMA issuers of tile A / B, each in uniform control flow with one lane elected once (one thread issues an MMA every
  * ~26 ns at best, which a single issuer for both tiles would be bound by).                                       */
 constexpr int kKeys3 = 64;
 constexpr int kK3Bytes = kKeys3 * 128 * 2;      /* one K tile = two sub-tiles [64 keys][64 dims]; one V^T tile = [128 dims][64 keys] */
@@ -490,11 +503,11 @@ constexpr int kPf3Smem = kOff3Bar + 512 + 1024;
  * consumed); SF, P [tile][buffer]; O [tile][last but one, last]: each completes once */
 enum { B3_Q = 0, B3_K0F = 1, B3_K0E = 3, B3_DF = 5, B3_DE = 9, B3_SF = 13, B3_P = 17, B3_O = 21 };
 constexpr unsigned kIdescN64 = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
-__device__ __forceinline__ void umma_f16_n64_elect(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
-    asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdescN64), "r"(accumulate) : "memory");
-}
 
+__device__ __forceinline__ void umma_f16_n64_lead(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate, unsigned lead) {
+    asm volatile("{\n .reg .pred p, e;\n setp.ne.b32 e, %5, 0;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdescN64), "r"(accumulate), "r"(lead) : "memory");
+}
 __global__ void __launch_bounds__(kPf3Threads, 1)
 hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
     extern __shared__ uint8_t s_raw[];
@@ -567,6 +580,9 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
          * order: S_x(0) S_x(1) | PV_x(0) S_x(2) | PV_x(1) S_x(3) | ...   tcgen05.commit covers what this thread issued, so
          * a K or V stage is released by one commit of each issuer */
         const int x = warp - 9;
+        /* one election for the whole walk: `lead` is 1 in the issuing lane (an elect.sync in front of every MMA and commit
+         * costs 1.7 % of the kernel) */
+        const unsigned lead = elect_one();
         bool ok = mbar_wait_blocking(BAR(B3_Q), 0u, s_abort, a.err, 20u);
         const unsigned long long dQ = make_desc(sbase + kOff3Q + x * kTileBytes);
         const unsigned long long dK0 = make_desc(sbase + kOff3K), dV0 = make_desc(sbase + kOff3V);
@@ -576,8 +592,8 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             const unsigned d = tm_sx + 64u * (j & 1);
 #pragma unroll
             for (int kk = 0; kk < 8; kk++)      /* the second half of d lies one sub-tile further on: 16 KB for Q, 8 KB for K */
-                umma_f16_n64_elect(d, dQ + (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2), k + (unsigned long long)((kk >> 2) * 512 + (kk & 3) * 2), kk > 0);
-            umma_commit_elect(BAR(B3_SF + 2 * x + (j & 1)));
+                umma_f16_n64_lead(d, dQ + (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2), k + (unsigned long long)((kk >> 2) * 512 + (kk & 3) * 2), kk > 0, lead);
+            umma_commit_lead(BAR(B3_SF + 2 * x + (j & 1)), lead);
         };
         /* tile B starts when the first softmax of tile A is through: half a period out of phase, the MMAs of one tile
          * run while the other tile's issuer is between two steps and its softmax warps have the SM's exponential
@@ -588,7 +604,7 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_qk(j);
-            umma_commit_elect(BAR(B3_K0E + j));
+            umma_commit_lead(BAR(B3_K0E + j), lead);
         }
         for (int j = 0; j < ntiles && ok; j++) {
             const int st = j & (kSt3 - 1), j2 = j + 2; const unsigned ph = (unsigned)(j / kSt3) & 1u;
@@ -607,15 +623,15 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 const unsigned pa = tm_sx + 64u * (j & 1);
                 const unsigned acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++) umma_f16_ta_elect(tm_ox, pa + 8u * kk, v + (unsigned long long)(kk * 2), kk > 0 ? 1u : acc0);
+                for (int kk = 0; kk < 4; kk++) umma_f16_ta_lead(tm_ox, pa + 8u * kk, v + (unsigned long long)(kk * 2), kk > 0 ? 1u : acc0, lead);
             }
             PF_TRACE3(j, x, 0);
             /* completion of P.V is only asked for directly at the end (last rescale, epilogue); before that the softmax
              * warps learn it from S_x(j+2), which this thread issues behind it */
-            if (j + 2 >= ntiles) umma_commit_elect(BAR(B3_O + 2 * x + (j + 1 == ntiles ? 1 : 0)));
+            if (j + 2 >= ntiles) umma_commit_lead(BAR(B3_O + 2 * x + (j + 1 == ntiles ? 1 : 0)), lead);
             PF_TRACE3(j, x, 1);
             if (j2 < ntiles) issue_qk(j2);
-            umma_commit_elect(BAR(B3_DE + st));
+            umma_commit_lead(BAR(B3_DE + st), lead);
             if (lane == 0) PF_TRACE(j, x, 7);
         }
     } else {

@@ -131,11 +131,12 @@ def test_committed_gpu_fixture(cuda, oracle):
         assert np.array_equal(make_slots(oracle, k, dt), g["kslots_" + dt])
 
 
+@pytest.mark.parametrize("heads", [(0, 8), (4, 4)])
 @pytest.mark.parametrize("dt", ["int8", "int4", "fp16"])
-def test_chunk_kernel_equals_row_kernel(cuda, oracle, dt):
+def test_chunk_kernel_equals_row_kernel(cuda, oracle, dt, heads):
     """Batches of 32 rows or more take the throughput-shaped kernel (one block per row for the queries, one block per KV
     head and 8 rows for K/V); smaller ones the per-row kernel.  Same rows, same slots and positions: identical cache
-    bytes and identical fp32 / fp16 queries."""
+    bytes and identical fp32 / fp16 queries -- also on a context that owns only KV heads 4..7."""
     import torch
     from hy3_b200 import Hy3Attn
     n, slot0 = 197, 3                         # not a multiple of 8, not aligned: the ragged last K/V block is covered
@@ -147,7 +148,7 @@ def test_chunk_kernel_equals_row_kernel(cuda, oracle, dt):
     tq, tk, tv = (torch.from_numpy(a).to(cuda) for a in (q, k, v))
     res = []
     for step in (n, 16):
-        ctx = Hy3Attn(kv_dtype=dt, n_layers=1, max_batch=n, max_tokens=512)
+        ctx = Hy3Attn(kv_dtype=dt, n_layers=1, max_batch=n, max_tokens=512, kv_head_begin=heads[0], kv_head_count=heads[1])
         ctx.set_norm_weights(0, w[0], w[1])
         qo = torch.empty((n, 64, 128), device=cuda)
         q16 = torch.empty((n, 64, 128), dtype=torch.float16, device=cuda)
