@@ -220,7 +220,8 @@ def batch_section(torch, dev, kind):
 def prefill_section(torch, dev, kv="fp16", prompt=8192, chunk=512):
     """Secondary metric: chunked causal prefill attention, an 8192-token prompt in 512-token chunks,
     FP16 KV cache, 64 Q / 8 KV heads, one layer (configs[2]).  TFLOP/s = 4*128*64*sum(pos+1) / device time
-    of the attention calls (fp16 gather pass + tcgen05 kernel); the fused append is timed separately."""
+    of the attention calls (conversion of pages not yet in the fp16 operand mirror, if any, + tcgen05 kernel); the fused
+    append -- which also writes the chunk's rows through into the mirror -- is timed separately and reported beside it."""
     from hy3_b200 import Hy3Attn
     ctx = Hy3Attn(kv_dtype=kv, n_layers=1, max_batch=chunk, max_tokens=prompt + 256, device=dev.index)
     q = torch.randn((prompt, H, D), device=dev)

@@ -63,7 +63,7 @@ struct hy3a_ctx {
     int *d_batch;         /* [3][max_batch] seq, slot, pos */
     float *d_partials;    /* decode scratch: [(ctas + max_batch*kv_heads)][8][130] */
     unsigned int *d_counters; /* decode scratch: [max_batch*kv_heads] arrival counters (self-resetting) */
-    void *d_pf_k, *d_pf_v; /* prefill: fp16 staging of dequantised K / V pages (INT8/INT4 caches) */
+    void *d_pf_k, *d_pf_v; /* prefill: fp16 operands shared by all layers, rebuilt per call (used when a layer has no mirror) */
     size_t pf_bytes;
     /* prefill operand mirrors: per layer, the fp16 tensor-core image (K rows, V transposed) of ONE sequence's tokens
      * [0, pf_mntok[layer]), kept across chunks so that a chunk only converts the pages it appended.  Any call that
