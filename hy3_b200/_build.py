@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhy3attn.so")
-SOURCES = ["append.cu", "decode.cu", "decode_tc.cu", "prefill.cu", "capi.cu", "selftest.cu"]
+SOURCES = ["append.cu", "decode.cu", "prefill.cu", "capi.cu", "selftest.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC,-fvisibility=default", "-I", os.path.join(ROOT, "include")]
 

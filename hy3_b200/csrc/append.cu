@@ -253,9 +253,9 @@ __global__ void __launch_bounds__(256) hy3a_fill_random_kernel(hy3a_cache_view c
 template <int DT>
 __global__ void hy3a_xport_kernel(hy3a_cache_view cache, int layer, int seq, int t0, int n, uint8_t *kslots, uint8_t *vslots, int import) {
     const hy3a_geom g = hy3a_make_geom(DT);
-    const int slot_bytes = (DT == 1 || DT == 3) ? 1040 : (DT == 2 ? 528 : 2048);
+    const int slot_bytes = DT == 1 ? 1040 : (DT == 2 ? 528 : 2048);
     const int hdr = DT == 0 ? 0 : 16;
-    const int head_bytes = (DT == 1 || DT == 3) ? 128 : (DT == 2 ? 64 : 256);
+    const int head_bytes = DT == 1 ? 128 : (DT == 2 ? 64 : 256);
     long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long total = (long long)n * 8 * 32 * 2;
     if (gid >= total) return;
@@ -267,8 +267,8 @@ __global__ void hy3a_xport_kernel(hy3a_cache_view cache, int layer, int seq, int
     int hl = head - cache.kv_head_begin;
     bool owned = hl >= 0 && hl < cache.kv_heads;
     int d0 = q4 * 4;
-    int sbytes = (DT == 1 || DT == 3) ? 4 : (DT == 2 ? 2 : 8); /* bytes of 4 dims in slot format */
-    uint8_t *sp = slot + hdr + head * head_bytes + ((DT == 1 || DT == 3) ? d0 : (DT == 2 ? d0 / 2 : d0 * 2));
+    int sbytes = DT == 1 ? 4 : (DT == 2 ? 2 : 8); /* bytes of 4 dims in slot format */
+    uint8_t *sp = slot + hdr + head * head_bytes + (DT == 1 ? d0 : (DT == 2 ? d0 / 2 : d0 * 2));
     if (!owned) {
         if (!import) { for (int b = 0; b < sbytes; b++) sp[b] = 0; if (DT != 0 && q4 == 0) { slot[head * 2] = 0; slot[head * 2 + 1] = 0; } }
         return;
@@ -278,15 +278,13 @@ __global__ void hy3a_xport_kernel(hy3a_cache_view cache, int layer, int seq, int
     /* byte locations of these 4 dims inside the page */
     uint8_t *pp[8];
     if (DT == 0) { int off = is_v ? g.v_off + hy3a_v16_dim_off(tok, d0) : hy3a_k_dim_off<0>(tok, d0); for (int b = 0; b < 8; b++) pp[b] = page + off + b; }
-    else if (DT == 3) {
-        for (int b = 0; b < 4; b++) pp[b] = page + (is_v ? g.v_off + hy3a_t_off(d0 + b, tok) : hy3a_t_off(tok, d0 + b));
-    } else if (DT == 1) {
+    else if (DT == 1) {
         if (!is_v) { int off = hy3a_k_dim_off<1>(tok, d0); for (int b = 0; b < 4; b++) pp[b] = page + off + b; }
         else { int o0 = g.v_off + hy3a_v_unit_off<1>(tok, d0), o1 = g.v_off + hy3a_v_unit_off<1>(tok, d0 + 2); pp[0] = page + o0; pp[1] = page + o0 + 1; pp[2] = page + o1; pp[3] = page + o1 + 1; }
     } else {
         int off = is_v ? g.v_off + hy3a_v_unit_off<2>(tok, d0) : hy3a_k_dim_off<2>(tok, d0); pp[0] = page + off; pp[1] = page + off + 1;
     }
-    const uint8_t flip = (is_v && DT != 0 && DT != 3) ? (DT == 1 ? 0x80 : 0x88) : 0x00;   /* V codes are stored offset-binary */
+    const uint8_t flip = (is_v && DT != 0) ? (DT == 1 ? 0x80 : 0x88) : 0x00;   /* V codes are stored offset-binary */
     for (int b = 0; b < sbytes; b++) { if (import) *pp[b] = sp[b] ^ flip; else sp[b] = *pp[b] ^ flip; }
     if (DT != 0 && q4 == 0) {
         uint8_t *sc = page + (is_v ? g.vs_off : g.ks_off) + tok * 2;
@@ -353,7 +351,6 @@ int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_str
         switch (ctx->geom.dtype) {
             case 0: e = cudaLaunchKernelEx(&cfg, hy3a_append_chunk_kernel<0>, cv, bv, ctx->rope, a, aligned8); break;
             case 1: e = cudaLaunchKernelEx(&cfg, hy3a_append_chunk_kernel<1>, cv, bv, ctx->rope, a, aligned8); break;
-            case 3: e = cudaLaunchKernelEx(&cfg, hy3a_append_chunk_kernel<3>, cv, bv, ctx->rope, a, aligned8); break;
             default: e = cudaLaunchKernelEx(&cfg, hy3a_append_chunk_kernel<2>, cv, bv, ctx->rope, a, aligned8); break;
         }
         ctx->launches++;
@@ -364,7 +361,6 @@ int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_str
     switch (ctx->geom.dtype) {
         case 0: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<0>, cv, bv, ctx->rope, a); break;
         case 1: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<1>, cv, bv, ctx->rope, a); break;
-        case 3: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<3>, cv, bv, ctx->rope, a); break;
         default: e = cudaLaunchKernelEx(&cfg, hy3a_append_kernel<2>, cv, bv, ctx->rope, a); break;
     }
     ctx->launches++;
@@ -382,7 +378,6 @@ int hy3a_launch_fill_random(hy3a_ctx *ctx, int layer, int seq, int t0, int n, ui
         switch (ctx->geom.dtype) {
             case 0: hy3a_fill_random_kernel<0><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0 + done, chunk, seed); break;
             case 1: hy3a_fill_random_kernel<1><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0 + done, chunk, seed); break;
-            case 3: hy3a_fill_random_kernel<3><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0 + done, chunk, seed); break;
             default: hy3a_fill_random_kernel<2><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0 + done, chunk, seed); break;
         }
         ctx->launches++;
@@ -401,7 +396,6 @@ int hy3a_launch_export(hy3a_ctx *ctx, int layer, int seq, int t0, int n, uint8_t
     switch (ctx->geom.dtype) {
         case 0: hy3a_xport_kernel<0><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0, n, d_kslots, d_vslots, import); break;
         case 1: hy3a_xport_kernel<1><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0, n, d_kslots, d_vslots, import); break;
-        case 3: hy3a_xport_kernel<3><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0, n, d_kslots, d_vslots, import); break;
         default: hy3a_xport_kernel<2><<<grid, block, 0, ctx->stream>>>(cv, layer, seq, t0, n, d_kslots, d_vslots, import); break;
     }
     ctx->launches++;

@@ -156,11 +156,7 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     ctx->shard_slot = -1;
     ctx->cfg.device = dev;
     ctx->device = dev;
-    {   /* INT8 caches have two page layouts: the tensor-core tile layout read by the tcgen05 decode kernel
-         * (HY3A_INT8_TC=1) and the pair layout read by the mma.sync kernel */
-        const char *e = getenv("HY3A_INT8_TC");
-        ctx->geom = hy3a_make_geom(cfg->kv_dtype == HY3A_KV_INT8 && e && atoi(e) ? 3 : cfg->kv_dtype);
-    }
+    ctx->geom = hy3a_make_geom(cfg->kv_dtype);
     ctx->sm_count = prop.multiProcessorCount;
     ctx->decode_ctas = prop.multiProcessorCount;
     { const char *e = getenv("HY3A_DECODE_CTAS"); if (e && atoi(e) > 0) ctx->decode_ctas = atoi(e); }

@@ -965,14 +965,10 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
     switch (ctx->geom.dtype) {
         case 0: e = launch_decode_dt<0>(ctx, cv, bv, a); break;
         case 1: e = launch_decode_dt<1>(ctx, cv, bv, a); break;
-        case 3: e = hy3a_launch_decode_tc(ctx, cv, bv, a); break;
         default: e = launch_decode_dt<2>(ctx, cv, bv, a); break;
     }
     ctx->launches++;
     ctx->bulk_write_pending = 0;   /* the kernel after this one only has this one to stay clear of */
-    if (e == cudaErrorNotSupported)
-        return hy3a_fail(ctx, HY3A_ESTATE, "decode: the tcgen05 INT8 path (HY3A_INT8_TC=1) serves batches with fewer (row, KV head) segments than CTAs (%d x %d >= %d)",
-                         ctx->batch_n, ctx->cfg.kv_head_count, ctx->decode_ctas);
     if (e != cudaSuccess) return hy3a_fail(ctx, HY3A_ECUDA, "decode launch: %s", cudaGetErrorString(e));
     return HY3A_OK;
 }
@@ -1027,7 +1023,6 @@ extern "C" int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, siz
     switch (ctx->geom.dtype) {
         case 0: e = launch_decode_dt<0>(ctx, cv, bv, a); break;
         case 1: e = launch_decode_dt<1>(ctx, cv, bv, a); break;
-        case 3: e = hy3a_launch_decode_tc(ctx, cv, bv, a); break;
         default: e = launch_decode_dt<2>(ctx, cv, bv, a); break;
     }
     ctx->launches++;

@@ -1,5 +1,5 @@
 /*
- * decode_common.cuh -- what the two decode kernels share: the argument block, the unit schedule
+ * decode_common.cuh -- helpers of the decode kernel: the argument block, the unit schedule
  * (segment / locate), shared-memory, mbarrier and bulk-copy primitives with bounded waits, and the
  * receiving side of the sequence-shard exchange.  Everything lives in an unnamed namespace: each
  * translation unit gets its own copy.
@@ -47,9 +47,6 @@ struct hy3a_decode_args {
     int stages;           /* staged variant: pages in the shared-memory ring (2..8) */
     int prefix_bytes;     /* bytes reserved for the page-count prefix */
 };
-
-/* the tcgen05 decode kernel for the tensor-core INT8 layout (decode_tc.cu) */
-cudaError_t hy3a_launch_decode_tc(hy3a_ctx *ctx, const hy3a_cache_view &cv, const hy3a_batch_view &bv, hy3a_decode_args &a);
 
 namespace {
 

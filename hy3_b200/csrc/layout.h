@@ -9,7 +9,6 @@
  *      [ K codes : 128 rows ][ V codes : 64 pair-rows (128 rows for FP16) ][ K scales fp16[128] ][ V scales fp16[128] ]
  *
  *   INT8  33 280 B   K row 128 B,  V pair-row 256 B
- *   INT8T 33 280 B   K tile 128 tokens x 128 B, V^T tile 128 dims x 128 B (internal layout 3, see hy3a_t_off)
  *   INT4  16 896 B   K row  64 B,  V pair-row 128 B
  *   FP16  65 536 B   K row 256 B,  V row      256 B, no scales
  *
@@ -41,7 +40,7 @@
 #define HY3A_PT 128 /* tokens per page */
 
 struct hy3a_geom {
-    int dtype;      /* 0 fp16, 1 int8, 2 int4, 3 int8 in the tensor-core tile layout (see hy3a_t_off) */
+    int dtype;      /* 0 fp16, 1 int8, 2 int4 */
     int k_row;      /* bytes per K row */
     int v_off;      /* byte offset of the V area */
     int v_prow;     /* bytes per V pair-row (INT8/INT4) or V row (FP16) */
@@ -53,8 +52,7 @@ struct hy3a_geom {
 HY3A_HD hy3a_geom hy3a_make_geom(int dtype) {
     hy3a_geom g;
     g.dtype = dtype;
-    if (dtype == 3) { g.k_row = 128; g.v_off = 16384; g.v_prow = 128; g.ks_off = 32768; g.vs_off = 33024; g.page_bytes = 33280; }
-    else if (dtype == 1) { g.k_row = 128; g.v_off = 16384; g.v_prow = 256; g.ks_off = 32768; g.vs_off = 33024; g.page_bytes = 33280; }
+    if (dtype == 1) { g.k_row = 128; g.v_off = 16384; g.v_prow = 256; g.ks_off = 32768; g.vs_off = 33024; g.page_bytes = 33280; }
     else if (dtype == 2) { g.k_row = 64; g.v_off = 8192; g.v_prow = 128; g.ks_off = 16384; g.vs_off = 16640; g.page_bytes = 16896; }
     else { g.k_row = 256; g.v_off = 32768; g.v_prow = 256; g.ks_off = 0; g.vs_off = 0; g.page_bytes = 65536; }
     return g;
@@ -88,11 +86,5 @@ template <int DT> HY3A_HD int hy3a_v_unit_off(int tok, int d) {
 /* ---- V (FP16 plain rows): offset relative to the V area of chunk `chunk` (8 halfs) of token tok. */
 HY3A_HD int hy3a_v16_chunk_off(int tok, int chunk) { return tok * 256 + ((chunk ^ (((tok >> 1) & 3) << 1)) << 4); }
 HY3A_HD int hy3a_v16_dim_off(int tok, int d) { return hy3a_v16_chunk_off(tok, d >> 3) + ((d & 7) << 1); }
-
-/* ---- layout 3 (INT8 for the tcgen05 decode kernel): the K area is a 128 x 128-byte tile, row = token, column =
- * head dim; the V area is the TRANSPOSED tile, row = head dim, column = token; both two's complement and both in
- * the tensor core's K-major 128-byte-swizzle order (16-byte chunk c of row r sits at chunk c ^ (r & 7)), so that a
- * page copied verbatim to 1024-byte-aligned shared memory is a valid tcgen05.mma operand.                        */
-HY3A_HD int hy3a_t_off(int row, int col) { return row * 128 + ((((col >> 4) ^ (row & 7))) << 4) + (col & 15); }
 
 #endif /* HY3A_LAYOUT_H */

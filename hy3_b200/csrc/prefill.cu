@@ -41,7 +41,6 @@
 namespace {
 
 constexpr int kQTok = 16;            /* query tokens per CTA (x 8 heads = 128 rows) */
-constexpr int kKeys = 128;           /* keys per K/V tile */
 constexpr int kTileBytes = 128 * 128 * 2;   /* one 128x128 fp16 operand tile = two 16 KB swizzled sub-tiles */
 constexpr float kScaleLog2 = 0.08838834764831845f * 1.4426950408889634f;   /* 1/sqrt(128) * log2(e) */
 constexpr float kPfThreshold = 8.f;
@@ -107,21 +106,8 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32
                    "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
                  : "memory");
 }
-/* issued by a whole warp in uniform control flow: the operands are computed by all lanes (so that they can live in the
- * uniform register file the instruction reads them from) and one elected lane issues */
-__device__ __forceinline__ void umma_f16_elect(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
-    asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
-}
-/* A operand in tensor memory (lane = row, 32-bit column c holds elements 2c and 2c+1 of the row's K slice) */
-__device__ __forceinline__ void umma_f16_ta_elect(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned accumulate) {
-    asm volatile("{\n .reg .pred p, e;\n elect.sync _|e, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n @e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit_elect(unsigned bar) {
-    asm volatile("{\n .reg .pred e;\n elect.sync _|e, 0xffffffff;\n @e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}" ::"r"(bar) : "memory");
-}
-/* the same with the election hoisted: `lead` is 1 in the lane a single elect.sync chose for the whole loop */
+/* The MMA issuers run in uniform control flow (the operands are then computed in the uniform data path the instruction
+ * reads them from) and one lane, elected once per walk, issues: `lead` is 1 in that lane. */
 __device__ __forceinline__ unsigned elect_one() {
     unsigned p;
     asm volatile("{\n .reg .pred e;\n elect.sync _|e, 0xffffffff;\n selp.u32 %0, 1, 0, e;\n}" : "=r"(p));
@@ -163,8 +149,8 @@ __global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cac
             } else {
                 const float s = __half2float(ks[tok]);
                 float f[8];
-                if (DT == 1 || DT == 3) {
-                    const uint2 w = *reinterpret_cast<const uint2 *>(page + (DT == 3 ? hy3a_t_off(tok, d) : hy3a_k_dim_off<1>(tok, d)));
+                if (DT == 1) {
+                    const uint2 w = *reinterpret_cast<const uint2 *>(page + hy3a_k_dim_off<1>(tok, d));
                     const unsigned ww[2] = {w.x, w.y};
 #pragma unroll
                     for (int i = 0; i < 8; i++) f[i] = (float)(signed char)((ww[i >> 2] >> (8 * (i & 3))) & 0xFF) * s;
@@ -191,8 +177,6 @@ __global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cac
             if (t < ntok) {
                 if (DT == 0) {
                     v = __half2float(*reinterpret_cast<const __half *>(page + g.v_off + hy3a_v16_dim_off(tok, d)));
-                } else if (DT == 3) {
-                    v = (float)(signed char)page[g.v_off + hy3a_t_off(d, tok)] * __half2float(vs[tok]);
                 } else if (DT == 1) {
                     const int b = page[g.v_off + hy3a_v_unit_off<1>(tok, d & ~1) + (d & 1)];
                     v = (float)(b - 128) * __half2float(vs[tok]);
@@ -212,287 +196,21 @@ struct prefill_args {
     size_t out_stride;
     int base, nq, kv_head_begin;
     unsigned *err;
-    unsigned long long *trace;   /* trace builds: time stamps of one CTA, [step][tile][8 events] */
 };
-#ifdef HY3A_DECODE_TRACE
-__device__ __forceinline__ unsigned long long pf_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define PF_TRACE(j, x, ev) do { if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (j) < 64) a.trace[((j) * 2 + (x)) * 8 + (ev)] = pf_gtime(); } while (0)
-#define PF_TRACE2(j, x, ev) do { if (lane == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (j) < 64) a.trace[1024 + ((j) * 2 + (x)) * 4 + (ev)] = pf_gtime(); } while (0)
-#define PF_TRACE3(j, x, ev) do { if (lane == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (j) < 64) a.trace[2048 + ((j) * 2 + (x)) * 2 + (ev)] = pf_gtime(); } while (0)
-#else
-#define PF_TRACE(j, x, ev) do { } while (0)
-#define PF_TRACE2(j, x, ev) do { } while (0)
-#define PF_TRACE3(j, x, ev) do { } while (0)
-#endif
 
-/* ---- pass 2, second generation: two Q tiles per CTA and P in tensor memory ---------------------------------------
- * One CTA = 32 query tokens x the 8 query heads of one KV head = two 128-row Q tiles, A and B, that share every K/V
- * tile.  Each tile has its own softmax warps, its own S (128 TMEM columns) and its own O (128 columns): 512 columns in
- * all.  While the softmax of tile A runs, the tensor core computes P_B.V_j and S_B for tile j+1, and so on: the
- * softmax of one tile hides behind the MMAs of the other, and the single issuing warp's fixed order keeps the two
- * tiles half a period out of phase.  P never touches shared memory: the softmax threads write it as packed fp16
- * pairs over the first 64 columns of their S (tcgen05.st) and P.V reads its A operand from tensor memory.  That
- * frees 64 KB of shared memory, which keeps K and V double-buffered beside the two Q tiles.                      */
-constexpr int kQTok2 = 32;                     /* query tokens per CTA = two tiles of kQTok */
-constexpr int kPf2SmWarps = 16;                /* softmax warps: tile x = warps with (warp / 4) % 2 == x; column half = warp / 8 */
-constexpr int kPf2Threads = 32 * kPf2SmWarps + 64;   /* + warp 16 = TMA producer, warp 17 = MMA issuer */
-constexpr int kOff2Q = 0, kOff2K = kOff2Q + 2 * kTileBytes, kOff2V = kOff2K + 2 * kTileBytes, kOff2Bar = kOff2V + 2 * kTileBytes;
-constexpr int kOff2Xch = kOff2Bar + 256;        /* float [2 tiles][2 halves][128 rows]: row maxima / denominators exchanged between the two halves */
-constexpr int kPf2Smem = kOff2Xch + 4096 + 1024;   /* maxima in the first 2 KB, denominators in the second */
-enum { B2_Q = 0, B2_KF = 1, B2_VF = 3, B2_KE = 5, B2_VE = 7, B2_SF = 9, B2_P = 11, B2_O = 13 };   /* [2] each except Q */
-
-__global__ void __launch_bounds__(kPf2Threads, 1)
-hy3a_prefill_kernel_v2(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, prefill_args a) {
-    extern __shared__ uint8_t s_raw[];
-    uint8_t *sm = s_raw + ((1024u - (smem_u32(s_raw) & 1023u)) & 1023u);
-    const unsigned sbase = smem_u32(sm);
-    const unsigned bar0 = sbase + kOff2Bar;
-    volatile unsigned *s_tmem = reinterpret_cast<volatile unsigned *>(sm + kOff2Bar + 192);
-    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kOff2Bar + 196);
-#define BAR(i) (bar0 + 8u * (unsigned)(i))
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q0 = blockIdx.x * kQTok2, hl = blockIdx.y;
-    const int kv_end = min(a.base + q0 + kQTok2, a.base + a.nq);   /* keys [0, kv_end) matter for this CTA */
-    const int ntiles = (kv_end + kKeys - 1) / kKeys;
-
-    if (tid == 0) {
-        *s_abort = 0;
-        mbar_init(BAR(B2_Q), 1);
-        for (int i = 0; i < 2; i++) {
-            mbar_init(BAR(B2_KF + i), 1); mbar_init(BAR(B2_VF + i), 1);
-            mbar_init(BAR(B2_KE + i), 1); mbar_init(BAR(B2_VE + i), 1);
-            mbar_init(BAR(B2_SF + i), 1); mbar_init(BAR(B2_P + i), 256); mbar_init(BAR(B2_O + i), 1);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {   /* one warp allocates all 512 TMEM columns (1 CTA per SM) */
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + kOff2Bar + 192), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const unsigned tmem = *s_tmem;
-    /* tile x: S at columns 128x (P over its first 64 columns), O at columns 256 + 128x */
-
-    if (warp == kPf2SmWarps) {
-        /* ===================== TMA producer ===================== */
-        if (lane == 0) {
-            /* programmatic dependent launch: everything above ran beside the tail of the conversion kernel; the
-             * operands are complete from here on (all global reads of this CTA follow this thread's copies) */
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-            mbar_expect_tx(BAR(B2_Q), 2 * kTileBytes);
-            for (int x = 0; x < 2; x++) {
-                tma_load_3d(sbase + kOff2Q + x * kTileBytes, &tm_q, BAR(B2_Q), 0, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
-                tma_load_3d(sbase + kOff2Q + x * kTileBytes + 16384, &tm_q, BAR(B2_Q), 64, (a.kv_head_begin + hl) * 8, q0 + x * kQTok);
-            }
-            for (int j = 0; j < ntiles; j++) {
-                const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
-                if (!mbar_wait_blocking(BAR(B2_KE + st), ph ^ 1u, s_abort, a.err, 10u)) break;
-                mbar_expect_tx(BAR(B2_KF + st), kTileBytes);
-                tma_load_3d(sbase + kOff2K + st * kTileBytes, &tm_k, BAR(B2_KF + st), 0, j * kKeys, hl);
-                tma_load_3d(sbase + kOff2K + st * kTileBytes + 16384, &tm_k, BAR(B2_KF + st), 64, j * kKeys, hl);
-                if (!mbar_wait_blocking(BAR(B2_VE + st), ph ^ 1u, s_abort, a.err, 11u)) break;
-                mbar_expect_tx(BAR(B2_VF + st), kTileBytes);
-                tma_load_3d(sbase + kOff2V + st * kTileBytes, &tm_v, BAR(B2_VF + st), j * kKeys, 0, hl);
-                tma_load_3d(sbase + kOff2V + st * kTileBytes + 16384, &tm_v, BAR(B2_VF + st), j * kKeys + 64, 0, hl);
-            }
-        }
-    } else if (warp == kPf2SmWarps + 1) {
-        /* ===================== MMA issuer =====================
-         * order: S_A(0) S_B(0) | PV_A(0) S_A(1) | PV_B(0) S_B(1) | PV_A(1) S_A(2) | ...
-         * S_x(j+1) overwrites the columns P_x(j) lives in, so it is issued behind PV_x(j) (the tensor core runs in order).
-         * The whole warp runs this code in uniform control flow and one elected lane issues: the descriptors are then
-         * computed once per warp in the uniform data path that tcgen05.mma reads its operands from, and the scalar code
-         * between two MMAs -- which is what bounds the issue rate of one thread -- shrinks to an add per operand */
-        bool ok = mbar_wait_blocking(BAR(B2_Q), 0u, s_abort, a.err, 20u);
-        const unsigned long long dQ[2] = {make_desc(sbase + kOff2Q), make_desc(sbase + kOff2Q + kTileBytes)};
-        const unsigned long long dK[2] = {make_desc(sbase + kOff2K), make_desc(sbase + kOff2K + kTileBytes)};
-        const unsigned long long dV[2] = {make_desc(sbase + kOff2V), make_desc(sbase + kOff2V + kTileBytes)};
-        auto issue_qk = [&](int x, int j) {      /* S_x(j) = Q_x . K_j^T : 8 k-steps of 16 over d = 128 */
-            const unsigned long long q = dQ[x], k = dK[j & 1];
-            const unsigned d = tmem + 128u * x;
-#pragma unroll
-            for (int kk = 0; kk < 8; kk++) {
-                const unsigned long long off = (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2);   /* (16 384 B | 32 B) >> 4 */
-                umma_f16_elect(d, q + off, k + off, kk > 0);
-            }
-            umma_commit_elect(BAR(B2_SF + x));
-        };
-        if (ok) ok = mbar_wait_blocking(BAR(B2_KF), 0u, s_abort, a.err, 21u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_qk(0, 0);
-            issue_qk(1, 0);
-            umma_commit_elect(BAR(B2_KE));
-        }
-        for (int j = 0; j < ntiles && ok; j++) {
-            const int st = j & 1; const unsigned ph = (unsigned)(j >> 1) & 1u;
-            const int st1 = (j + 1) & 1; const unsigned ph1 = (unsigned)((j + 1) >> 1) & 1u;
-            for (int x = 0; x < 2 && ok; x++) {
-                if (x == 0) ok = mbar_wait_blocking(BAR(B2_VF + st), ph, s_abort, a.err, 23u);
-                if (ok) ok = mbar_wait_blocking(BAR(B2_P + x), (unsigned)j & 1u, s_abort, a.err, 24u);   /* P_x(j) in tensor memory, O_x rescaled */
-                if (ok && j + 1 < ntiles && x == 0) ok = mbar_wait_blocking(BAR(B2_KF + st1), ph1, s_abort, a.err, 25u);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                if (lane == 0) PF_TRACE(j, x, 6);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                /* O_x += P_x(j) . V_j : 8 k-steps of 16 keys; A = 8 columns of packed fp16 pairs per step */
-                {
-                    const unsigned long long v = dV[st];
-                    const unsigned d = tmem + 256u + 128u * x, pa = tmem + 128u * x;
-                    const unsigned acc0 = j > 0 ? 1u : 0u;
-#pragma unroll
-                    for (int kk = 0; kk < 8; kk++) {
-                        const unsigned long long off = (unsigned long long)((kk >> 2) * 1024 + (kk & 3) * 2);
-                        umma_f16_ta_elect(d, pa + 8u * kk, v + off, kk > 0 ? 1u : acc0);
-                    }
-                }
-                umma_commit_elect(BAR(B2_O + x));
-                if (x == 1) umma_commit_elect(BAR(B2_VE + st));
-                if (j + 1 < ntiles) {
-                    issue_qk(x, j + 1);
-                    if (x == 1) umma_commit_elect(BAR(B2_KE + st1));
-                }
-                if (lane == 0) PF_TRACE(j, x, 7);
-            }
-        }
-    } else {
-        /* ===================== softmax warps: tile x = (warp / 4) % 2, column half hf = warp / 8; thread = (row of Q
-         * tile x, 64 of its 128 key columns).  The two threads of a row exchange their maxima through shared memory. */
-        const int x = (warp >> 2) & 1, hf = warp >> 3, r = tid & 127, t_local = r >> 3, h = r & 7;
-        const int tq0 = q0 + x * kQTok;                          /* first query token of this tile */
-        const int qpos = a.base + tq0 + t_local;                 /* global index of this row's query */
-        const bool row_valid = (tq0 + t_local) < a.nq;
-        const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16; /* this warp's quarter of the TMEM lanes */
-        const unsigned tm_s = tmem + 128u * x, tm_o = tmem + 256u + 128u * x;
-        float *xch = reinterpret_cast<float *>(sm + kOff2Xch) + x * 256;   /* [2 halves][128 rows] */
-        float m = -INFINITY, l = 0.f;    /* l: this thread's half of the row's denominator */
-        bool ok = true;
-        for (int j = 0; j < ntiles && ok; j++) {
-            ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B2_SF + x), (unsigned)j & 1u, s_abort, a.err, 30u));   /* keep the warp together */
-            const bool tr = (warp & 11) == 0 && lane == 0;   /* trace builds: the first warp of each tile */
-            if (tr) PF_TRACE(j, x, 0);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int k0 = j * kKeys + 64 * hf;                    /* first key of this thread's columns */
-            const bool masked = (j * kKeys + kKeys - 1 > a.base + tq0);   /* the tile crosses the diagonal of some row */
-            unsigned v0[32], v1[32];
-            tmem_ld32_nowait(tm_s + lane_base + 64u * hf, v0);
-            tmem_ld32_nowait(tm_s + lane_base + 64u * hf + 32u, v1);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (tr) PF_TRACE(j, x, 1);
-            /* the maximum is taken over the raw scores (the scale is positive) and the scale is folded into the exponent's
-             * argument: one FFMA per element instead of a multiply and a subtract */
-            float mx = -INFINITY;
-            if (masked) {      /* only the tiles on the diagonal pay for the causal test */
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    if (k0 + i > qpos) v0[i] = 0xff800000u;
-                    if (k0 + 32 + i > qpos) v1[i] = 0xff800000u;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i++) mx = fmax3(mx, __uint_as_float(v0[i]), __uint_as_float(v1[i]));
-            xch[hf * 128 + r] = mx;
-            asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
-            mx = fmaxf(mx, xch[(hf ^ 1) * 128 + r]) * kScaleLog2;
-            if (tr) PF_TRACE(j, x, 2);
-            const bool grow = mx > m + kPfThreshold;              /* true while m == -inf (key 0 is never masked) */
-            const float m_new = grow ? mx : m;
-            const float neg_m = -m_new;
-            unsigned pk[32];
-            float lsum = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                /* the denominator sums the unrounded values: the fp16 rounding of P is a zero-mean 2^-12 relative error per
-                 * term, far below the tolerance */
-                const float e0 = ex2f(fmaf(__uint_as_float(v0[i]), kScaleLog2, neg_m)), e1 = ex2f(fmaf(__uint_as_float(v0[i + 1]), kScaleLog2, neg_m));
-                const float e2 = ex2f(fmaf(__uint_as_float(v1[i]), kScaleLog2, neg_m)), e3 = ex2f(fmaf(__uint_as_float(v1[i + 1]), kScaleLog2, neg_m));
-                pk[i >> 1] = pack_h2(e0, e1); pk[16 + (i >> 1)] = pack_h2(e2, e3);
-                lsum += (e0 + e1) + (e2 + e3);
-            }
-            if (tr) PF_TRACE(j, x, 3);
-            /* O_x is only ours again when P_x(j-1).V_(j-1) has completed */
-            if (j > 0 && ok) {
-                ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B2_O + x), (unsigned)(j - 1) & 1u, s_abort, a.err, 31u));
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            /* tcgen05.ld / .st are warp-collective: the whole warp rescales its 32 rows (this thread: 64 of the 128 output
-             * dims) as soon as one of them moved its reference (the others multiply by exactly 1) */
-            if (tr) PF_TRACE(j, x, 4);
-            const float alpha = grow ? ex2f(m - m_new) : 1.f;     /* 0 on the first tile (m = -inf) */
-            if (__any_sync(0xffffffffu, grow)) {
-                l *= alpha;
-                if (j > 0) {
-#pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        unsigned v[32];
-                        tmem_ld32(tm_o + lane_base + 64u * hf + 32u * c, v);
-#pragma unroll
-                        for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st32(tm_o + lane_base + 64u * hf + 32u * c, v);
-                    }
-                }
-                m = m_new;
-            }
-            l += lsum;
-            /* P over the first 64 columns of S (column c = keys 2c, 2c+1): this thread's 64 keys are columns 32 hf .. 32 hf + 31.
-             * Both halves have read their S columns (the barrier above), so the overwrite is safe. */
-            tmem_st32(tm_s + lane_base + 32u * hf, pk);
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(BAR(B2_P + x));
-            if (tr) PF_TRACE(j, x, 5);
-        }
-        /* epilogue: O / l, l = sum of the two halves */
-        xch[512 + hf * 128 + r] = l;
-        asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
-        l += xch[512 + (hf ^ 1) * 128 + r];
-        if (ok && ntiles > 0) ok = mbar_wait_blocking(BAR(B2_O + x), (unsigned)(ntiles - 1) & 1u, s_abort, a.err, 32u);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__all_sync(0xffffffffu, ok) && ntiles > 0) {      /* warp-uniform: tcgen05.ld is warp-collective */
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            float *orow = a.out + (size_t)(tq0 + t_local) * a.out_stride + (size_t)((a.kv_head_begin + hl) * 8 + h) * HY3A_D + 64 * hf;
-#pragma unroll
-            for (int c = 0; c < 2; c++) {
-                unsigned v[32];
-                tmem_ld32(tm_o + lane_base + 64u * hf + 32u * c, v);
-                if (row_valid)
-#pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    *reinterpret_cast<float4 *>(orow + 32 * c + i) = make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
-                                                                                   __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-            }
-        }
-    }
-    /* ---- common exit: everybody arrives here, also after a wait ran out; release TMEM */
-    if (*s_abort && warp == kPf2SmWarps && lane == 0) {
-        /* copies already issued must land before the shared memory goes away */
-        for (int st = 0; st < 2; st++)
-            for (unsigned ph = 0; ph < 2; ph++)
-                for (unsigned spin = 0; spin < (1u << 12) && !mbar_test(BAR(B2_KF + st), ph) && !mbar_test(BAR(B2_VF + st), ph); spin++) __nanosleep(64);
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
-#undef BAR
-}
-
-/* ---- pass 2, third generation: 64-key tiles, S double-buffered -------------------------------------------------------
- * Same CTA shape as the second generation (two 128-row Q tiles A and B = 32 query tokens x 8 heads, P in tensor
- * memory), but a K/V tile is 64 keys, so that each Q tile has TWO S buffers (2 x 64 TMEM columns) beside its O (128
+/* ---- pass 2: the attention kernel -------------------------------------------------------------------------------------
+ * One CTA = 32 query tokens x the 8 query heads of one KV head = two 128-row Q tiles A and B that share every K/V tile
+ * (GQA packing); P lives in tensor memory.  A K/V tile is 64 keys, so that each Q tile has TWO S buffers (2 x 64 TMEM columns) beside its O (128
  * columns): 2 x 256 = 512 columns.  S_x(j+2) is issued right behind P_x(j).V_j into the buffer P_x(j) lives in, i.e. the
  * scores of a step are computed while the softmax of the step before runs, and the loop
  *      S ready -> softmax -> P -> P.V -> next S
- * of the second generation, whose length bounded it, falls apart into a softmax chain (one thread per row, 64 columns
+ * falls apart into a softmax chain (one thread per row, 64 columns
  * per step, no exchange between threads) and an MMA chain that only meet at the P and S barriers.  The softmax warps
  * wait for P.V only when a row's reference maximum moved (lazy rescale of O) and at the end.
  * Warps 0-3 / 4-7: softmax of tile A / B; warp 8: TMA producer (4-stage rings of 16 KB K and V tiles); warps 9 / 10:
  * MMA issuers of tile A / B, each in uniform control flow with one lane elected once (one thread issues an MMA every
  * ~26 ns at best, which a single issuer for both tiles would be bound by).                                       */
+constexpr int kQTok2 = 32;                     /* query tokens per CTA = two tiles of kQTok */
 constexpr int kKeys3 = 64;
 constexpr int kK3Bytes = kKeys3 * 128 * 2;      /* one K tile = two sub-tiles [64 keys][64 dims]; one V^T tile = [128 dims][64 keys] */
 constexpr int kSt3 = 4;                         /* ring stages */
@@ -608,14 +326,10 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         for (int j = 0; j < ntiles && ok; j++) {
             const int st = j & (kSt3 - 1), j2 = j + 2; const unsigned ph = (unsigned)(j / kSt3) & 1u;
-            PF_TRACE2(j, x, 0);
             ok = mbar_wait_blocking(BAR(B3_DF + st), ph, s_abort, a.err, 23u);                                               /* V_j and K_(j+2) */
-            PF_TRACE2(j, x, 1);
             if (ok) ok = mbar_wait_blocking(BAR(B3_P + 2 * x + (j & 1)), (unsigned)(j >> 1) & 1u, s_abort, a.err, 24u);   /* P_x(j) in tensor memory, O_x rescaled */
-            PF_TRACE2(j, x, 3);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (lane == 0) PF_TRACE(j, x, 6);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             /* O_x += P_x(j) . V_j : 4 k-steps of 16 keys; A = 8 columns of packed fp16 pairs per step */
             {
@@ -625,14 +339,11 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++) umma_f16_ta_lead(tm_ox, pa + 8u * kk, v + (unsigned long long)(kk * 2), kk > 0 ? 1u : acc0, lead);
             }
-            PF_TRACE3(j, x, 0);
             /* completion of P.V is only asked for directly at the end (last rescale, epilogue); before that the softmax
              * warps learn it from S_x(j+2), which this thread issues behind it */
             if (j + 2 >= ntiles) umma_commit_lead(BAR(B3_O + 2 * x + (j + 1 == ntiles ? 1 : 0)), lead);
-            PF_TRACE3(j, x, 1);
             if (j2 < ntiles) issue_qk(j2);
             umma_commit_lead(BAR(B3_DE + st), lead);
-            if (lane == 0) PF_TRACE(j, x, 7);
         }
     } else {
         /* ===================== softmax warps: tile x = warp / 4; thread = one row of Q tile x ===================== */
@@ -647,8 +358,6 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int j = 0; j < ntiles && ok; j++) {
             const unsigned tm_s = tmem + 128u * x + 64u * (j & 1) + lane_base;
             ok = __all_sync(0xffffffffu, mbar_wait_blocking(BAR(B3_SF + 2 * x + (j & 1)), (unsigned)(j >> 1) & 1u, s_abort, a.err, 30u));   /* keep the warp together */
-            const bool tr = (warp & 3) == 0 && lane == 0;   /* trace builds: the first warp of each tile */
-            if (tr) PF_TRACE(j, x, 0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int k0 = j * kKeys3;
             const bool masked = (k0 + kKeys3 - 1 > a.base + tq0);   /* the tile crosses the diagonal of some row */
@@ -656,7 +365,6 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tmem_ld32_nowait(tm_s, v0);
             tmem_ld32_nowait(tm_s + 32u, v1);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (tr) PF_TRACE(j, x, 1);
             if (masked) {      /* only the tiles on the diagonal pay for the causal test */
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
@@ -670,7 +378,6 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
             for (int i = 0; i < 32; i++) mx4[i & 3] = fmax3(mx4[i & 3], __uint_as_float(v0[i]), __uint_as_float(v1[i]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kScaleLog2;
-            if (tr) PF_TRACE(j, x, 2);
             /* a tile that is masked for the whole row (its keys all lie behind the row's query; only in the last tiles of
              * the CTA) has mx = -inf: nothing moves and all its P are 0 */
             const bool grow = mx > m + kPfThreshold;              /* true while m == -inf (key 0 is never masked) */
@@ -688,7 +395,6 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 ls[0] += e0; ls[1] += e1; ls[2] += e2; ls[3] += e3;
             }
             const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
-            if (tr) PF_TRACE(j, x, 3);
             /* tcgen05.ld / .st are warp-collective: the whole warp rescales its 32 rows as soon as one of them moved its
              * reference (the others multiply by exactly 1).  O_x is only ours when P_x(j-1).V_(j-1) has completed. */
             const float alpha = grow ? ex2f(m - m_new) : 1.f;     /* 0 on the first tile (m = -inf) */
@@ -712,7 +418,6 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 l *= alpha;
                 m = m_new;
             }
-            if (tr) PF_TRACE(j, x, 4);
             l += lsum;
             /* P over the first 32 columns of this S buffer (column c = keys 2c, 2c+1) */
             tmem_st32(tm_s, pk);
@@ -720,7 +425,6 @@ hy3a_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(B3_P + 2 * x + (j & 1)));
-            if (tr) PF_TRACE(j, x, 5);
         }
         /* epilogue: O / l.  The issuer commits P.V of the last two tiles on barriers of their own, which therefore complete
          * exactly once (a parity wait on a barrier that runs through many phases can only tell the last completed phase
@@ -850,7 +554,6 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
         __half *wk = (__half *)ws_k, *wv = (__half *)ws_v;
         cudaError_t e;
         switch (ctx->geom.dtype) {
-            case 3: e = cudaLaunchKernelEx(&cfg, hy3a_kv_to_f16_kernel<3>, cv, layer, seq, pg0, ntok, tok_stride, wk, wv); break;
             case 0: e = cudaLaunchKernelEx(&cfg, hy3a_kv_to_f16_kernel<0>, cv, layer, seq, pg0, ntok, tok_stride, wk, wv); break;
             case 1: e = cudaLaunchKernelEx(&cfg, hy3a_kv_to_f16_kernel<1>, cv, layer, seq, pg0, ntok, tok_stride, wk, wv); break;
             default: e = cudaLaunchKernelEx(&cfg, hy3a_kv_to_f16_kernel<2>, cv, layer, seq, pg0, ntok, tok_stride, wk, wv); break;
@@ -859,12 +562,7 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
         HY3A_CUDA(ctx, e);
     }
 
-    { const char *e = getenv("HY3A_PF_STOP"); if (e && atoi(e) == 1) return HY3A_OK; }   /* development: pass 1 only */
-    /* HY3A_PF_GEN=2: the second-generation kernel (128-key tiles, one S buffer per Q tile); default 3: 64-key tiles, S
-     * double-buffered */
-    int gen = 3;
-    { const char *e = getenv("HY3A_PF_GEN"); if (e && atoi(e) == 2) gen = 2; }
-    const int keys = gen == 3 ? kKeys3 : kKeys;
+    const int keys = kKeys3;
     CUtensorMap tq, tk, tv;
     {
         const cuuint64_t dq[3] = {HY3A_D, HY3A_N_HEAD, (cuuint64_t)nq}, sq[2] = {HY3A_D * 2, HY3A_N_HEAD * HY3A_D * 2};
@@ -883,19 +581,17 @@ int hy3a_launch_prefill(hy3a_ctx *ctx, int layer, int seq, int base_slot, int nq
     static bool attr_dev[64];   /* function attributes are per device */
     bool &attr_set = attr_dev[ctx->device & 63];
     if (!attr_set) {
-        HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize, kPf2Smem));
         HY3A_CUDA(ctx, cudaFuncSetAttribute(hy3a_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPf3Smem));
         attr_set = true;
     }
     prefill_args a;
-    a.out = out; a.out_stride = out_stride; a.base = base_slot; a.nq = nq; a.kv_head_begin = ctx->cfg.kv_head_begin; a.err = ctx->d_err; a.trace = ctx->d_trace;
+    a.out = out; a.out_stride = out_stride; a.base = base_slot; a.nq = nq; a.kv_head_begin = ctx->cfg.kv_head_begin; a.err = ctx->d_err;
     {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((nq + kQTok2 - 1) / kQTok2, kvh); cfg.stream = ctx->stream;
-        cfg.blockDim = dim3(gen == 3 ? kPf3Threads : kPf2Threads); cfg.dynamicSmemBytes = gen == 3 ? kPf3Smem : kPf2Smem;
+        cfg.blockDim = dim3(kPf3Threads); cfg.dynamicSmemBytes = kPf3Smem;
         cfg.attrs = attr; cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-        if (gen == 3) HY3A_CUDA(ctx, cudaLaunchKernelEx(&cfg, hy3a_prefill_kernel, tq, tk, tv, a));
-        else HY3A_CUDA(ctx, cudaLaunchKernelEx(&cfg, hy3a_prefill_kernel_v2, tq, tk, tv, a));
+        HY3A_CUDA(ctx, cudaLaunchKernelEx(&cfg, hy3a_prefill_kernel, tq, tk, tv, a));
     }
     ctx->launches++;
     ctx->bulk_write_pending = 1;

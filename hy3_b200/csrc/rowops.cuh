@@ -42,7 +42,7 @@ __device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g,
     float m = fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3])));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const float qmax = (DT == 1 || DT == 3) ? 127.f : 7.f;
+    const float qmax = DT == 1 ? 127.f : 7.f;
     float s = __fadd_rn(__fdiv_rn(m, qmax), 1e-8f);
     float inv = __fdiv_rn(1.f, s);
     int c[4];
@@ -52,15 +52,7 @@ __device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g,
     __half sh = __float2half(s);
     unsigned sbits = (unsigned)__half_as_ushort(sh);
     if (lane == 0) *reinterpret_cast<unsigned short *>((scale_page ? scale_page : page) + (is_v ? g.vs_off : g.ks_off) + tok * 2) = (unsigned short)sbits;
-    if (DT == 3) {
-        if (!is_v) {
-            unsigned w = (unsigned)(c[0] & 0xFF) | ((unsigned)(c[1] & 0xFF) << 8) | ((unsigned)(c[2] & 0xFF) << 16) | ((unsigned)(c[3] & 0xFF) << 24);
-            *reinterpret_cast<unsigned *>(page + hy3a_t_off(tok, d0)) = w;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; j++) page[g.v_off + hy3a_t_off(d0 + j, tok)] = (uint8_t)(c[j] & 0xFF);
-        }
-    } else if (DT == 1) {
+    if (DT == 1) {
         if (!is_v) {
             unsigned w = (unsigned)(c[0] & 0xFF) | ((unsigned)(c[1] & 0xFF) << 8) | ((unsigned)(c[2] & 0xFF) << 16) | ((unsigned)(c[3] & 0xFF) << 24);
             *reinterpret_cast<unsigned *>(page + hy3a_k_dim_off<1>(tok, d0)) = w;

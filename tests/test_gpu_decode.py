@@ -16,16 +16,12 @@ def load_cache(ctx, oracle, dt, layer, seq, K, V):
     return slots_to_float(oracle, ks, dt), slots_to_float(oracle, vs, dt)
 
 
-@pytest.fixture(params=["staged", "direct", "tc"])
+@pytest.fixture(params=["staged", "direct"])
 def variant(request, monkeypatch):
-    """The load paths of the mma.sync decode kernel (bulk-copy ring in shared memory, or direct 128-bit loads) and,
-    for INT8 caches, the tcgen05 kernel with its tensor-core page layout (other cache types ignore the switch)."""
+    """The two load paths of the decode kernel: bulk-copy ring in shared memory, or direct 128-bit loads."""
     monkeypatch.delenv("HY3A_DECODE_STAGES", raising=False)
-    monkeypatch.delenv("HY3A_INT8_TC", raising=False)
     if request.param == "direct":
         monkeypatch.setenv("HY3A_DECODE_STAGES", "0")
-    elif request.param == "tc":
-        monkeypatch.setenv("HY3A_INT8_TC", "1")
     return request.param
 
 
@@ -33,8 +29,6 @@ def variant(request, monkeypatch):
 def test_decode_lengths(cuda, oracle, dt, variant):
     import torch
     from hy3_b200 import Hy3Attn
-    if variant == "tc" and dt != "int8":
-        pytest.skip("the tcgen05 decode kernel serves INT8 caches")
     nmax = max(LENS)
     ctx = Hy3Attn(kv_dtype=dt, n_layers=3, max_batch=4, max_tokens=nmax + 256)
     K = oracle.fill_normal((nmax, 8, 128), SEED, 51)
@@ -60,8 +54,6 @@ def test_decode_long_context_many_ctas(cuda, oracle, dt, variant):
     """Long enough that every CTA gets work and (row, head) segments span many CTAs (merge epilogue)."""
     import torch
     from hy3_b200 import Hy3Attn
-    if variant == "tc" and dt != "int8":
-        pytest.skip("the tcgen05 decode kernel serves INT8 caches")
     n = 40000
     ctx = Hy3Attn(kv_dtype=dt, n_layers=1, max_batch=2, max_tokens=n + 128)
     K = oracle.fill_normal((n, 8, 128), SEED, 61)
@@ -78,11 +70,8 @@ def test_decode_long_context_many_ctas(cuda, oracle, dt, variant):
     ctx.close()
 
 
-@pytest.mark.parametrize("tc", [False, True])
-def test_decode_ragged_batch_and_poison(cuda, oracle, monkeypatch, tc):
-    """Several sequences of different lengths in one launch; cache bytes past each length are poison.
-    tc: through the tcgen05 kernel and its page layout."""
-    monkeypatch.setenv("HY3A_INT8_TC", "1" if tc else "0")
+def test_decode_ragged_batch_and_poison(cuda, oracle):
+    """Several sequences of different lengths in one launch; cache bytes past each length are poison."""
     import torch
     from hy3_b200 import Hy3Attn
     lens = [1, 130, 257, 1000, 77, 128, 3000]
@@ -107,14 +96,11 @@ def test_decode_ragged_batch_and_poison(cuda, oracle, monkeypatch, tc):
     ctx.close()
 
 
-@pytest.mark.parametrize("tc", [False, True])
-def test_decode_many_segments_share_ctas(cuda, oracle, monkeypatch, tc):
+def test_decode_many_segments_share_ctas(cuda, oracle):
     """More (row, KV head) segments than CTAs: every CTA walks through several segments and segments straddle CTAs
     (the equal-unit-range schedule); a fused step, so that the appends land in many different CTAs."""
     import torch
     from hy3_b200 import Hy3Attn
-    from hy3_b200 import Hy3AttnError
-    monkeypatch.setenv("HY3A_INT8_TC", "1" if tc else "0")
     rng = np.random.default_rng(7)
     lens0 = [int(x) for x in rng.integers(1, 900, size=40)]      # 320 segments for 148 CTAs
     lens0[3], lens0[17] = 0, 2600
@@ -123,14 +109,6 @@ def test_decode_many_segments_share_ctas(cuda, oracle, monkeypatch, tc):
     for s_, n0 in enumerate(lens0):
         if n0:
             ctx.fill_random(0, s_, 0, n0, 500 + s_)
-    if tc:
-        # the opt-in tcgen05 kernel refuses schedules in which a CTA serves pieces of several segments (a code, not a hang)
-        ctx.batch_set(list(range(B)), [n0 for n0 in lens0])
-        with pytest.raises(Hy3AttnError) as ei:
-            ctx.decode(0, torch.zeros((B, 64, 128), device=cuda))
-        assert ei.value.code == -5
-        ctx.close()
-        return
     q = oracle.fill_normal((2, B, 64, 128), SEED, 331)
     k = oracle.fill_normal((2, B, 8, 128), SEED, 332)
     v = oracle.fill_normal((2, B, 8, 128), SEED, 333)
@@ -186,13 +164,10 @@ def test_append_then_decode_end_to_end(cuda, oracle):
     ctx.close()
 
 
-@pytest.mark.parametrize("dt", ["int8", "int4", "fp16", "int8-tc"])
-def test_fused_step_equals_append_plus_decode(cuda, oracle, dt, monkeypatch):
+@pytest.mark.parametrize("dt", ["int8", "int4", "fp16"])
+def test_fused_step_equals_append_plus_decode(cuda, oracle, dt):
     """hy3a_decode_step (one kernel) against hy3a_append + hy3a_decode: identical cache bytes, identical
-    queries, identical outputs; a ragged batch so that page and granule boundaries are crossed.
-    int8-tc: the tcgen05 kernel (its producer warp performs the fused append)."""
-    monkeypatch.setenv("HY3A_INT8_TC", "1" if dt == "int8-tc" else "0")
-    dt = dt.split("-")[0]
+    queries, identical outputs; a ragged batch so that page and granule boundaries are crossed."""
     import torch
     from hy3_b200 import Hy3Attn
     lens0 = [0, 15, 16, 127, 128, 300, 2000]          # tokens already cached per sequence

@@ -115,10 +115,3 @@ def test_prefill_chunks_reuse_converted_pages(cuda, oracle, dt, monkeypatch):
     want = oracle.prefill_causal(qf, Kf, Vf, base, rows=[0, n - 1])
     for i in (0, n - 1):
         check_attention(out[i], want[i], "%s before cut: base=%d row %d" % (dt, base, i))
-
-
-def test_prefill_second_generation_kernel(cuda, oracle, monkeypatch):
-    """HY3A_PF_GEN=2 selects the kernel with 128-key tiles and one S buffer per Q tile (kept for comparison)."""
-    monkeypatch.setenv("HY3A_PF_GEN", "2")
-    run_case(cuda, oracle, "fp16", 127, 130)
-    run_case(cuda, oracle, "int8", 256, 256, rows=[0, 1, 127, 128, 255])
