@@ -1,9 +1,15 @@
-"""In-tree build of libhy3attn.so (CUDA kernels + C ABI) for sm_100a with nvcc.
+"""In-tree build of the two shared libraries for sm_100a with nvcc.
 
     python -m hy3_b200._build [--force] [--verbose]
 
-Objects go to build/ (git-ignored), the shared library next to this file so that it
-travels with the source tree.  nvcc cross-compiles without a GPU.
+  libhy3attn.so   the attention library: CUDA kernels + the C ABI of include/hy3_attn.h
+  libhy3_gpu.so   the same objects plus hy3_gpu_dropin.cu: hy3_gpu_init / hy3_gpu_free / hy3_eval_gpu for the reference
+                  engine (include/hy3_gpu_dropin.h).  It is compiled against the engine's own hy3.h, so it needs the
+                  engine's checkout: HY3_REF, or a directory `reference` next to this repository.  Without one a
+                  prebuilt libhy3_gpu.so is kept as it is.
+
+Objects go to build/ (git-ignored), the libraries next to this file so that they travel with the source tree.  nvcc
+cross-compiles without a GPU.
 """
 import os
 import subprocess
@@ -13,6 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhy3attn.so")
+DROPIN_LIB = os.path.join(HERE, "libhy3_gpu.so")
 SOURCES = ["append.cu", "decode.cu", "prefill.cu", "capi.cu", "selftest.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC,-fvisibility=default", "-I", os.path.join(ROOT, "include")]
@@ -57,7 +64,42 @@ def build(force=False, verbose=False, defines=(), lib_path=None):
         if r.returncode:
             print(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    if not defines and lib_path is None:
+        build_dropin(objs, headers, nvcc, obj_dir, force, verbose)
     return lib_out
+
+
+def reference_dir():
+    """The reference engine's checkout (for its hy3.h), or None."""
+    for d in (os.environ.get("HY3_REF"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if d and os.path.exists(os.path.join(d, "hy3.h")):
+            return d
+    return None
+
+
+def build_dropin(attn_objs, headers, nvcc, obj_dir, force=False, verbose=False):
+    ref = reference_dir()
+    if ref is None:
+        if not os.path.exists(DROPIN_LIB):
+            print("hy3_b200._build: no reference checkout (HY3_REF) and no prebuilt %s: the drop-in backend is not built" % DROPIN_LIB)
+        return None
+    src = os.path.join(CSRC, "hy3_gpu_dropin.cu")
+    obj = os.path.join(obj_dir, "hy3_gpu_dropin.o")
+    if force or _newer([src, os.path.join(ref, "hy3.h")] + headers, obj):
+        cmd = [nvcc] + NVCC_FLAGS + ["-I", ref] + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode or verbose:
+            print("---- nvcc hy3_gpu_dropin.cu\n" + r.stdout + r.stderr)
+        if r.returncode:
+            raise RuntimeError("nvcc failed")
+    if force or _newer(attn_objs + [obj], DROPIN_LIB):
+        # hy3_rope_get_params and forward_layer_* stay undefined: the engine the library is linked into provides them
+        cmd = [nvcc, "-shared", "-o", DROPIN_LIB, obj] + attn_objs + ["-cudart", "static", "-lcublas"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode:
+            print(r.stdout + r.stderr)
+            raise RuntimeError("link failed")
+    return DROPIN_LIB
 
 
 if __name__ == "__main__":

@@ -330,6 +330,14 @@ int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_str
     /* rows that extend the sequence whose prefill operands this layer keeps, gap-free: convert them here, where they are
      * in registers, instead of reading the pages back in the conversion kernel */
     a.mirror_k = a.mirror_v = NULL; a.mirror_stride = 0;
+    if (k_in && ctx->batch_n > 0) {
+        /* rows that rewrite slots the layer's operands already cover (a second append of the same batch, corrected K/V):
+         * the covered part is stale from the lowest rewritten slot on */
+        int lowest = ctx->batch_slot0;
+        if (!ctx->batch_contig) lowest = ctx->batch_slot_min;
+        if (ctx->batch_seq_uniform) hy3a_mirror_truncate(ctx, ctx->batch_seq0, layer, lowest);
+        else { ctx->pf_mntok[layer] = 0; }
+    }
     if (k_in && ctx->pf_mk[layer] && ctx->batch_contig && ctx->batch_seq0 == ctx->pf_mseq && ctx->batch_slot0 == ctx->pf_mntok[layer] &&
         ctx->batch_slot0 + ctx->batch_n <= ctx->pf_mcap[layer]) {
         a.mirror_k = (__half *)ctx->pf_mk[layer]; a.mirror_v = (__half *)ctx->pf_mv[layer]; a.mirror_stride = ctx->pf_mcap[layer];

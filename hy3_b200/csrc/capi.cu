@@ -16,7 +16,7 @@
 
 #include "ctx.h"
 
-static char g_create_err[512];
+static thread_local char g_create_err[512];   /* message of the last failed hy3a_create of this thread */
 
 int hy3a_fail(hy3a_ctx *ctx, int code, const char *fmt, ...) {
     va_list ap;
@@ -171,6 +171,11 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
         const char *e = getenv("HY3A_DECODE_STAGES");
         if (e) { int v = atoi(e); if (v < ctx->decode_stages) ctx->decode_stages = v; }
     }
+    struct device_guard {   /* the caller's current device is put back on every way out */
+        int prev;
+        device_guard() : prev(-1) { cudaGetDevice(&prev); }
+        ~device_guard() { if (prev >= 0) cudaSetDevice(prev); }
+    } guard;
     CREATE_CUDA(cudaSetDevice(dev));
     CREATE_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
     ctx->own_stream = 1;
@@ -190,9 +195,9 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     CREATE_CUDA(cudaMalloc(&ctx->d_norm_w, (size_t)cfg->n_layers * 2 * HY3A_D * sizeof(float)));
     CREATE_CUDA(cudaMalloc(&ctx->d_batch, (size_t)3 * cfg->max_batch * sizeof(int)));
     ctx->partial_records = (size_t)ctx->decode_ctas + (size_t)cfg->max_batch * cfg->kv_head_count;
-    CREATE_CUDA(cudaMalloc(&ctx->d_partials, ctx->partial_records * 8 * HY3A_PARTIAL_FLOATS * sizeof(float)));
-    CREATE_CUDA(cudaMalloc(&ctx->d_counters, (size_t)cfg->max_batch * cfg->kv_head_count * sizeof(unsigned)));
-    CREATE_CUDA(cudaMemsetAsync(ctx->d_counters, 0, (size_t)cfg->max_batch * cfg->kv_head_count * sizeof(unsigned), ctx->stream));
+    CREATE_CUDA(cudaMalloc(&ctx->d_partials, ctx->partial_records * 8 * HY3A_REC_FLOATS * sizeof(float)));
+    CREATE_CUDA(cudaMalloc(&ctx->d_counters, (size_t)2 * cfg->max_batch * cfg->kv_head_count * sizeof(unsigned)));
+    CREATE_CUDA(cudaMemsetAsync(ctx->d_counters, 0, (size_t)2 * cfg->max_batch * cfg->kv_head_count * sizeof(unsigned), ctx->stream));
     CREATE_CUDA(cudaMalloc(&ctx->d_trace, (size_t)512 * 64 * sizeof(unsigned long long)));
     CREATE_CUDA(cudaMemsetAsync(ctx->d_trace, 0, (size_t)512 * 64 * sizeof(unsigned long long), ctx->stream));
     CREATE_CUDA(cudaMalloc(&ctx->d_err, HY3A_ERR_WORDS * sizeof(unsigned)));
@@ -251,6 +256,8 @@ int hy3a_sync(hy3a_ctx *ctx) {
     if (ctx->h_err[0]) {
         unsigned code = ctx->h_err[0], where = ctx->h_err[1], w2 = ctx->h_err[2], w3 = ctx->h_err[3];
         cudaMemsetAsync(ctx->d_err, 0, HY3A_ERR_WORDS * sizeof(unsigned), ctx->stream);
+        /* a kernel that gave up may have left merge counters behind */
+        cudaMemsetAsync(ctx->d_counters, 0, (size_t)2 * ctx->cfg.max_batch * ctx->cfg.kv_head_count * sizeof(unsigned), ctx->stream);
         return hy3a_fail(ctx, HY3A_ETIMEOUT, "device-side bounded wait or bounds check failed (code %u, where %u, detail %u %u)", code, where, w2, w3);
     }
     return HY3A_OK;
@@ -361,6 +368,11 @@ int hy3a_batch_set(hy3a_ctx *ctx, int n, const int *seq_ids, const int *slots, c
     ctx->batch_n = n;
     ctx->batch_seq0 = seq_ids[0]; ctx->batch_slot0 = slots[0]; ctx->batch_contig = slots[0] >= 0;
     for (int i = 1; i < n && ctx->batch_contig; i++) ctx->batch_contig = seq_ids[i] == seq_ids[0] && slots[i] == slots[0] + i;
+    ctx->batch_seq_uniform = 1; ctx->batch_slot_min = slots[0] < 0 ? 0 : slots[0];
+    for (int i = 1; i < n; i++) {
+        if (seq_ids[i] != seq_ids[0]) ctx->batch_seq_uniform = 0;
+        if (slots[i] >= 0 && slots[i] < ctx->batch_slot_min) ctx->batch_slot_min = slots[i];
+    }
     return HY3A_OK;
 }
 
@@ -369,6 +381,9 @@ static int check_layer(hy3a_ctx *ctx, int layer, const char *who) {
     if (!ctx) return HY3A_EINVAL;
     if (layer < 0 || layer >= ctx->cfg.n_layers) return hy3a_fail(ctx, HY3A_EINVAL, "%s: layer %d out of range [0,%d)", who, layer, ctx->cfg.n_layers);
     if (ctx->batch_n < 1) return hy3a_fail(ctx, HY3A_ESTATE, "%s: no batch set (call hy3a_batch_set first)", who);
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != ctx->device)
+        return hy3a_fail(ctx, HY3A_ESTATE, "%s: the context lives on device %d but device %d is current (cudaSetDevice first)", who, ctx->device, cur);
     return 0;
 }
 
@@ -422,7 +437,7 @@ int hy3a_shard_init(hy3a_ctx *ctx, int rank, int world, int n_slots, int n_rows,
     const size_t n_seg = (size_t)n_rows * ctx->cfg.kv_head_count;
     const size_t slice = n_seg * 8 * (HY3A_PARTIAL_FLOATS / 2) * 16;    /* flagged 16-byte lines: 2 values each */
     ctx->shard_state_off = ((size_t)n_slots * world * slice + 255) & ~(size_t)255;
-    ctx->shard_bytes = ctx->shard_state_off + (size_t)n_slots * n_seg * sizeof(unsigned);   /* use count per (slot, segment) */
+    ctx->shard_bytes = ctx->shard_state_off + (size_t)n_slots * n_seg * 8 * sizeof(unsigned);   /* use count per (slot, segment, head) */
     HY3A_CUDA(ctx, cudaMalloc(&ctx->shard_local, ctx->shard_bytes));
     HY3A_CUDA(ctx, cudaMemset(ctx->shard_local, 0, ctx->shard_bytes));
     cudaIpcMemHandle_t h;

@@ -13,6 +13,7 @@
 #define HY3A_DECODE_WARPS 11
 #endif
 #define HY3A_ERR_WORDS 4
+#define HY3A_REC_FLOATS 132   /* a head's {m, l, acc[128]} record in the merge scratch, padded to a multiple of 16 bytes */
 #define HY3A_RING_SLOTS 16
 
 /* Everything a kernel needs to address the cache; passed by value. */
@@ -61,8 +62,8 @@ struct hy3a_ctx {
     float *d_inv_freq;
     float *d_norm_w;      /* [n_layers][2][128] */
     int *d_batch;         /* [3][max_batch] seq, slot, pos */
-    float *d_partials;    /* decode scratch: [(ctas + max_batch*kv_heads)][8][130] */
-    unsigned int *d_counters; /* decode scratch: [max_batch*kv_heads] arrival counters (self-resetting) */
+    float *d_partials;    /* decode scratch: [(ctas + max_batch*kv_heads)][8][HY3A_REC_FLOATS] */
+    unsigned int *d_counters; /* decode scratch: [2][max_batch*kv_heads] arrival / finished-fold counters (self-resetting) */
     void *d_pf_k, *d_pf_v; /* prefill: fp16 operands shared by all layers, rebuilt per call (used when a layer has no mirror) */
     size_t pf_bytes;
     /* prefill operand mirrors: per layer, the fp16 tensor-core image (K rows, V transposed) of ONE sequence's tokens
@@ -90,6 +91,7 @@ struct hy3a_ctx {
     unsigned int *h_err;  /* pinned */
     int batch_n;
     int batch_contig, batch_seq0, batch_slot0;   /* the batch is rows slot0, slot0+1, ... of one sequence (a prefill chunk) */
+    int batch_seq_uniform, batch_slot_min;       /* all rows belong to batch_seq0; lowest slot >= 0 of the batch */
     int decode_ctas;
     int bulk_write_pending; /* a kernel that wrote many KV slots was enqueued and no decode launch has followed it yet */
     int use_pdl;          /* launch kernels with programmatic stream serialization (HY3A_NO_PDL=1 turns it off) */

@@ -53,6 +53,7 @@ constexpr int kFixedML = ((kWarps * 8 * 2 * 4) + 127) / 128 * 128;
 constexpr int kFixedQ = 8 * 32 * 16;
 constexpr int kFixed = kFixedO + kFixedML + kFixedQ;   /* bytes of shared memory in front of the page-count prefix */
 constexpr bool kPSplit = true;                         /* carry the fp16 residual of P in MMA rows 8-15 */
+constexpr int kRecFloats = HY3A_REC_FLOATS;             /* floats per head record in the merge scratch (130 used) */
 constexpr int kShardBatch = 5;                          /* ranks polled at once by the sharded epilogue */
 static_assert(kShardBatch * 8 * (HY3A_PARTIAL_FLOATS / 2) * 16 <= kFixedO, "landing zone of the rank records exceeds the staging area");
 constexpr float kRescaleThreshold = 8.f;               /* lazy rescale: the running max may lag by 2^8 */
@@ -87,19 +88,10 @@ __device__ __forceinline__ unsigned pack_h2(float lo, float hi) {
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
-__device__ __forceinline__ float2 unpack_h2(unsigned v) {
-    __half2 h = *reinterpret_cast<__half2 *>(&v);
-    return __half22float2(h);
-}
 __device__ __forceinline__ void mma16816(float c[4], const unsigned a[4], unsigned b0, unsigned b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void imma16832(int c[4], const uint4 &a, unsigned b0, unsigned b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
 
 /* ---- exact integer-code -> fp16x2 conversions of V --------------------------------------
@@ -129,10 +121,6 @@ __device__ __forceinline__ unsigned cvt_u4_hi(unsigned x) {
  * 16+4tig..16+4tig+3) carry head dims kdim32<DT>(kk, tig, 0..7).  In both cases these are
  * exactly the dims whose codes the thread gets out of its own 16-byte loads.              */
 __device__ __forceinline__ int kdim16(int j, int tig, int s) { int c = tig + 4 * (j >> 1); return 8 * c + 4 * (j & 1) + s; }
-template <int DT> __device__ __forceinline__ int kdim32(int kk, int tig, int s) {
-    if (DT == 1) return 16 * (tig + 4 * (s >> 2)) + 4 * kk + (s & 3);   /* chunk tig / tig+4, word kk */
-    return 32 * tig + 8 * kk + 2 * (s & 3) + (s >> 2);                   /* word kk: even nibbles, then odd nibbles */
-}
 /* ---- output-dimension map of P.V: n-block jn (0..15), column n (0..7) -> head dim. */
 template <int DT> __device__ __forceinline__ int vdim(int jn, int n) {
     if (DT == 2) return 16 * n + jn;
@@ -450,7 +438,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
              * when the other ranks' records are due */
             if (is_producer) continue;
             for (int e = tid; e < G * 8; e += kThreads) {
-                const unsigned flag = a.shard_round[i * G + (e >> 3)] + 1u;
+                const unsigned flag = a.shard_round[i * G * 8 + e] + 1u;
                 for (int r = 0; r < a.n_dest; r++)
                     if (r != a.my_rank) shard_store_line(a.dest[r] + ((size_t)i * G * 8 + e) * kShardLines, -INFINITY, 0.f, flag);
             }
@@ -746,43 +734,63 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
         const size_t head_q = (size_t)(cache.kv_head_begin + hl) * 8 + h; /* global query head */
         u = sg.seg_u0 + sg.p_end;
 
+        /* Which of the 8 heads this CTA finishes (writes out / exchanges): all of them, unless the fold of a
+         * segment is spread over several of its CTAs (below). */
+        int h_lo = 0, h_hi = 8;
         if (npieces > 1) {
             if (red) {
-                float *rec = a.scratch + ((size_t)(cta + rec_base) * 8 + h) * HY3A_PARTIAL_FLOATS;
+                float *rec = a.scratch + ((size_t)(cta + rec_base) * 8 + h) * kRecFloats;
                 if (d4 == 0) { rec[0] = M; rec[1] = L; }
                 rec[2 + d4] = acc[0]; rec[3 + d4] = acc[1]; rec[4 + d4] = acc[2]; rec[5 + d4] = acc[3];
             }
-            __threadfence();   /* every writer orders its part of the record before the arrival below */
-            consumer_sync();
-            if (tid == 0) {
-                unsigned old = atomicAdd(a.counters + sidx, 1u);
-                s_flag = (old == (unsigned)(npieces - 1));
-            }
-            consumer_sync();
-            if (warp == 0) TRACE(25);
-            if (!s_flag) continue;   /* CTA-uniform */
-            __threadfence();
-            /* last arrival: fold all pieces with the rule of hy3_gpu.cu:233-247.  The pieces' records
-             * (4160 contiguous bytes each) are fetched into shared memory with 16-byte asynchronous
-             * copies issued by all threads at once -- one L2 round trip for the whole segment instead
-             * of one per piece -- and folded from there.  Landing zone: the page ring when this CTA
-             * has no more pages to stream (always so when segments are CTA-aligned), else the merge
-             * buffer; larger segments go through it in several rounds.                              */
-            const bool ring_idle = STAGED && aligned;
-            const unsigned land = ring_idle ? ring_base : smem_u32(s_dyn);
-            const float *land_g = reinterpret_cast<const float *>(ring_idle ? s_dyn + kFixed + a.prefix_bytes + 128 : s_dyn);
-            const int land_cap = (ring_idle ? a.stages * geom.page_bytes : kFixedO) / (8 * HY3A_PARTIAL_FLOATS * 4);
-            M = -INFINITY; L = 0.f; acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-            for (int c0 = 0; c0 < npieces; c0 += land_cap) {
-                const int nc = min(land_cap, npieces - c0);
-                const uint8_t *src = reinterpret_cast<const uint8_t *>(a.scratch + (size_t)(c_first + c0 + rec_base) * 8 * HY3A_PARTIAL_FLOATS);
-                for (int i = tid; i < nc * 260; i += kThreads)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(land + 16u * (unsigned)i), "l"(src + 16 * (size_t)i) : "memory");
-                asm volatile("cp.async.wait_all;" ::: "memory");
+            consumer_sync();   /* the record is complete in CTA scope; the release below publishes it */
+            if (STAGED && aligned && a.spread) {
+                /* ---- CTA-aligned segments (small batches): the fold is SPREAD.  Every CTA announces its record on
+                 * the segment's arrival counter; the first F pieces then each fold 8/F of the heads over all pieces
+                 * (one warp per head: 33 16-byte asynchronous copies per record and lane 0 one more, all records in
+                 * flight at once, landing in the idle page ring), instead of one CTA pulling every head of every
+                 * piece while the others have left.  The remaining pieces leave at once.                          */
+                const int F = npieces >= 8 ? 8 : (npieces >= 4 ? 4 : 2), hpf = 8 / F, piece = cta - c_first;
+                if (tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.counters + sidx) : "memory");
+                TRACE(25);
+                if (piece >= F) continue;   /* CTA-uniform */
+                if (tid == 0) {
+                    /* bounded wait for the other pieces (they are resident: one CTA per SM at most) */
+                    unsigned seen = 0;
+                    unsigned long long t0 = 0;
+                    bool ok = false;
+                    for (unsigned i = 0; i < (1u << 24); i++) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.counters + sidx) : "memory");
+                        if (seen >= (unsigned)npieces) { ok = true; break; }
+                        if ((i & 255u) == 255u) {
+                            unsigned long long t1;
+                            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                            if (t0 == 0) t0 = t1;
+                            if (s_abort || (i >= (1u << 14) && t1 - t0 > 500000000ull)) break;
+                        }
+                    }
+                    if (!ok) { s_abort = 1; if (atomicCAS(a.err, 0u, 4u) == 0u) { a.err[1] = 50u; a.err[2] = blockIdx.x; a.err[3] = seen; } }
+                    s_flag = ok;
+                }
                 consumer_sync();
-                if (red) {
-                    for (int c = 0; c < nc; c++) {
-                        const float *pr = land_g + ((size_t)c * 8 + h) * HY3A_PARTIAL_FLOATS;
+                h_lo = piece * hpf; h_hi = h_lo + hpf;
+                const bool mine = red && h >= h_lo && h < h_hi;
+                M = -INFINITY; L = 0.f; acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                if (s_flag && mine) {
+                    /* landing zone of head h: npieces x 528 bytes in the ring (idle: this CTA's pages are consumed) */
+                    const unsigned zone = (unsigned)((h - h_lo) * npieces) * (unsigned)(kRecFloats * 4);
+                    const uint8_t *src = reinterpret_cast<const uint8_t *>(a.scratch + ((size_t)c_first * 8 + h) * kRecFloats);
+                    for (int c = 0; c < npieces; c++) {
+                        const unsigned dst = ring_base + zone + (unsigned)c * (unsigned)(kRecFloats * 4);
+                        const uint8_t *g = src + (size_t)c * 8 * kRecFloats * 4;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * (unsigned)lane), "l"(g + 16 * lane) : "memory");
+                        if (lane == 0) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512u), "l"(g + 512) : "memory");
+                    }
+                    asm volatile("cp.async.wait_all;" ::: "memory");
+                    __syncwarp();
+                    const float *zf = reinterpret_cast<const float *>(s_dyn + kFixed + a.prefix_bytes + 128 + zone);
+                    for (int c = 0; c < npieces; c++) {
+                        const float *pr = zf + (size_t)c * kRecFloats;
                         const float pm = pr[0], pl = pr[1];
                         if (!(pl > 0.f)) continue;
                         const float2 v01 = *reinterpret_cast<const float2 *>(pr + 2 + d4), v23 = *reinterpret_cast<const float2 *>(pr + 4 + d4);
@@ -793,19 +801,65 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                         M = nm;
                     }
                 }
-                if (c0 + land_cap < npieces) consumer_sync();   /* landing zone is reused */
+                consumer_sync();   /* every landing zone is read (the sharded exchange lands its lines in the ring too) */
+                if (tid == 0) {
+                    /* the last of the F folders puts both counters back to zero for the next launch */
+                    const unsigned old = atomicAdd(a.counters + a.n_counters + sidx, 1u);
+                    if (old == (unsigned)(F - 1)) { a.counters[sidx] = 0u; a.counters[a.n_counters + sidx] = 0u; }
+                }
+                TRACE(26);
+            } else {
+                /* ---- a CTA may hold pieces of several segments (large batches): the LAST CTA to arrive folds, nobody waits */
+                if (tid == 0) {
+                    unsigned old;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(a.counters + sidx) : "memory");
+                    s_flag = (old == (unsigned)(npieces - 1));
+                }
+                consumer_sync();
+                TRACE(25);
+                if (!s_flag) continue;   /* CTA-uniform */
+                /* fold all pieces with the rule of hy3_gpu.cu:233-247.  The pieces' records (contiguous) are fetched
+                 * into the merge buffer with 16-byte asynchronous copies issued by all threads at once and folded
+                 * from there; larger segments go through it in several rounds.                                    */
+                const unsigned land = smem_u32(s_dyn);
+                const float *land_g = reinterpret_cast<const float *>(s_dyn);
+                const int land_cap = kFixedO / (8 * kRecFloats * 4);
+                M = -INFINITY; L = 0.f; acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                for (int c0 = 0; c0 < npieces; c0 += land_cap) {
+                    const int nc = min(land_cap, npieces - c0);
+                    const uint8_t *src = reinterpret_cast<const uint8_t *>(a.scratch + (size_t)(c_first + c0 + rec_base) * 8 * kRecFloats);
+                    for (int i = tid; i < nc * (8 * kRecFloats / 4); i += kThreads)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(land + 16u * (unsigned)i), "l"(src + 16 * (size_t)i) : "memory");
+                    asm volatile("cp.async.wait_all;" ::: "memory");
+                    consumer_sync();
+                    if (red) {
+                        for (int c = 0; c < nc; c++) {
+                            const float *pr = land_g + ((size_t)c * 8 + h) * kRecFloats;
+                            const float pm = pr[0], pl = pr[1];
+                            if (!(pl > 0.f)) continue;
+                            const float2 v01 = *reinterpret_cast<const float2 *>(pr + 2 + d4), v23 = *reinterpret_cast<const float2 *>(pr + 4 + d4);
+                            const float nm = fmaxf(M, pm), os = ex2(M - nm), rs = ex2(pm - nm);
+                            L = L * os + pl * rs;
+                            acc[0] = acc[0] * os + v01.x * rs; acc[1] = acc[1] * os + v01.y * rs;
+                            acc[2] = acc[2] * os + v23.x * rs; acc[3] = acc[3] * os + v23.y * rs;
+                            M = nm;
+                        }
+                    }
+                    if (c0 + land_cap < npieces) consumer_sync();   /* landing zone is reused */
+                }
+                if (tid == 0) a.counters[sidx] = 0u; /* self-reset for the next launch */
+                consumer_sync();   /* the landing zone is read; the next segment may reuse the buffer */
+                TRACE(26);
             }
-            if (tid == 0) a.counters[sidx] = 0u; /* self-reset for the next launch */
-            consumer_sync();   /* the landing zone is read; the next segment may reuse the buffer */
-            if (warp == 0) TRACE(26);
         }
+        const bool fin = red && h >= h_lo && h < h_hi;   /* this thread finishes its (head, 4 dims) of the segment */
         if (SHARD) {
             /* sequence sharding: this rank's records of the segment go into every other rank's gather buffer as
              * flagged lines (no fence, no separate flag: a line is valid when both of its flag words carry this
              * use's number), then the same threads collect the other ranks' lines and finish the segment */
             const int seg = row * G + hl;
-            if (red) {
-                const unsigned flag = a.shard_round[seg] + 1u;
+            if (fin) {
+                const unsigned flag = a.shard_round[seg * 8 + h] + 1u;   /* use count of this (slot, segment, head) */
                 const float m_nat = M * kLn2;
                 const size_t ro = ((size_t)seg * 8 + h) * kShardLines;
                 for (int r = 0; r < a.n_dest; r++) {
@@ -830,12 +884,13 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     shard_fold<kShardBatch>(fa);
                 }
                 if (warp == 0) TRACE(30);
+                __syncwarp();                /* every lane of the head's warp has read the use count */
+                if (d4 == 0) a.shard_round[seg * 8 + h] = flag;
             }
-            consumer_sync();                 /* every thread has read the use count */
-            if (tid == 0) a.shard_round[seg] += 1u;
+            consumer_sync();                 /* the landing zones may be reused by the next segment */
             continue;
         }
-        if (!red) continue;
+        if (!fin) continue;
         if (a.user_partials) {
             float *rec = a.user_partials + ((size_t)row * G * 8 + (size_t)hl * 8 + h) * HY3A_PARTIAL_FLOATS;
             if (d4 == 0) { rec[0] = M * kLn2; rec[1] = L; } /* m in natural-log units like the reference record */
@@ -857,12 +912,13 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     shard_fold_args fa;
                     fa.rec0 = a.gathered + ((size_t)seg * 8 + h) * kShardLines; fa.rank_stride = (size_t)n * G * 8 * kShardLines; fa.err = a.err;
                     fa.out = a.out + (size_t)i * a.out_stride + ((size_t)(cache.kv_head_begin + hl) * 8 + h) * HY3A_D + d4;
-                    fa.n_ranks = a.n_dest; fa.my_rank = a.my_rank; fa.line_a = 1 + (d4 >> 1); fa.flag = a.shard_round[seg] + 1u; fa.stage = reinterpret_cast<const uint4 *>(s_dyn); fa.h = h; fa.lane = lane;
+                    fa.n_ranks = a.n_dest; fa.my_rank = a.my_rank; fa.line_a = 1 + (d4 >> 1); fa.flag = a.shard_round[seg * 8 + h] + 1u; fa.stage = reinterpret_cast<const uint4 *>(s_dyn); fa.h = h; fa.lane = lane;
                     fa.own_m = -INFINITY; fa.own_l = 0.f; fa.own_acc[0] = fa.own_acc[1] = fa.own_acc[2] = fa.own_acc[3] = 0.f;
                     shard_fold<kShardBatch>(fa);
+                    __syncwarp();
+                    if (d4 == 0) a.shard_round[seg * 8 + h] = fa.flag;
                 }
                 consumer_sync();
-                if (tid == 0) a.shard_round[seg] += 1u;
             }
         }
 }
@@ -934,13 +990,17 @@ int hy3a_decode_ring_capacity(int page_bytes, int max_batch) {
 }
 /* Largest grid the last-arrival merge can stage in the merge buffer. */
 int hy3a_decode_max_ctas(void) { return kFixedO / 64; }
+static_assert(kRecFloats >= HY3A_PARTIAL_FLOATS && (kRecFloats * 4) % 16 == 0, "a head's record must start on a 16-byte boundary");
 
 int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride, float *partials,
                        const hy3a_step_inputs *step) {
     decode_args a;
     memset(&a, 0, sizeof(a));
     a.q = q; a.q_stride = q_stride; a.out = out; a.out_stride = out_stride; a.user_partials = partials;
-    a.scratch = ctx->d_partials; a.counters = ctx->d_counters; a.err = ctx->d_err; a.layer = layer;
+    a.scratch = ctx->d_partials; a.counters = ctx->d_counters; a.n_counters = ctx->cfg.max_batch * ctx->cfg.kv_head_count; a.err = ctx->d_err; a.layer = layer;
+    /* the spread fold pays off where the epilogue is the cross-GPU exchange (8 CTAs store to the peers instead of one);
+     * its folders wait for the other pieces, so every CTA of the grid must be resident */
+    a.spread = ctx->shard_slot >= 0 && ctx->decode_ctas <= ctx->sm_count;
     a.trace = ctx->d_trace;
     a.early_prefetch = ctx->use_pdl && !ctx->bulk_write_pending;
     if (ctx->shard_slot >= 0) {   /* set by hy3a_decode_step_sharded around this call */
@@ -950,7 +1010,7 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
         a.n_dest = W; a.my_rank = ctx->shard_rank;
         for (int r = 0; r < W; r++) a.dest[r] = reinterpret_cast<uint4 *>(ctx->shard_peer[r]) + ((size_t)slot * W + ctx->shard_rank) * slice;
         a.gathered = reinterpret_cast<const uint4 *>(ctx->shard_local) + (size_t)slot * W * slice;
-        a.shard_round = reinterpret_cast<unsigned *>(ctx->shard_local + ctx->shard_state_off) + (size_t)slot * n_seg;
+        a.shard_round = reinterpret_cast<unsigned *>(ctx->shard_local + ctx->shard_state_off) + (size_t)slot * n_seg * 8;
     }
     if (step) {
         a.fused = 1;
@@ -976,12 +1036,12 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
 /* ---- decode without any allocation ---------------------------------------------------------
  * Scratch for hy3a_decode_noalloc: the records and arrival counters of the cross-CTA merge live in
  * this file-scope device array instead of buffers the context allocated.  Every GPU that loads the
- * library holds these 2.6 MB until the process exits.  Layout: [kNoAllocRecords][8][130] floats of
- * records, then kNoAllocCounters arrival counters.                                               */
+ * library holds these 2.4 MB until the process exits.  Layout: [kNoAllocRecords][8][132] floats of
+ * records, then two counters (arrivals, finished folds) per segment.                                               */
 constexpr int kNoAllocRows = 64;                                   /* most (batch row, KV head) segments per call */
 constexpr int kNoAllocRecords = 512 + kNoAllocRows;                /* one per CTA of the largest grid + one per segment */
-constexpr size_t kNoAllocRecordBytes = (size_t)kNoAllocRecords * 8 * HY3A_PARTIAL_FLOATS * sizeof(float);
-static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocRecordBytes + kNoAllocRows * sizeof(unsigned)];
+constexpr size_t kNoAllocRecordBytes = (size_t)kNoAllocRecords * 8 * kRecFloats * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocRecordBytes + 2 * kNoAllocRows * sizeof(unsigned)];
 static unsigned char *g_noalloc_ptr[64];                           /* device address of the array, per device ordinal */
 
 extern "C" int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride, float *out, size_t out_stride) {
@@ -995,26 +1055,29 @@ extern "C" int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, siz
                          ctx->batch_n, ctx->cfg.kv_head_count, kNoAllocRows);
     if (ctx->decode_ctas > 512) return hy3a_fail(ctx, HY3A_EINVAL, "decode_noalloc: grid of %d CTAs exceeds the built-in scratch", ctx->decode_ctas);
     if (ctx->device < 0 || ctx->device >= 64) return hy3a_fail(ctx, HY3A_EINVAL, "decode_noalloc: device ordinal %d not supported", ctx->device);
-    if (!g_noalloc_ptr[ctx->device]) {
-        /* one-time set-up on this device: in host code the array's name is only a handle, the kernel
-         * needs the device address                                                                 */
+    {   /* the launch below goes to the current device: it must be the context's */
         int cur = -1;
         HY3A_CUDA(ctx, cudaGetDevice(&cur));
-        if (cur != ctx->device) HY3A_CUDA(ctx, cudaSetDevice(ctx->device));
+        if (cur != ctx->device)
+            return hy3a_fail(ctx, HY3A_ESTATE, "decode_noalloc: the context lives on device %d but device %d is current (cudaSetDevice first)", ctx->device, cur);
+    }
+    if (!g_noalloc_ptr[ctx->device]) {
+        /* one-time set-up on this device (it is current): in host code the array's name is only a handle, the
+         * kernel needs the device address                                                                  */
         void *p = NULL;
         cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-        if (cur != ctx->device) cudaSetDevice(cur);
         if (e != cudaSuccess || !p) return hy3a_fail(ctx, HY3A_ECUDA, "decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
         g_noalloc_ptr[ctx->device] = (unsigned char *)p;
     }
     unsigned char *scratch = g_noalloc_ptr[ctx->device];
     /* the arrival counters must start at zero; a call that was cut short may have left some behind */
-    HY3A_CUDA(ctx, cudaMemsetAsync(scratch + kNoAllocRecordBytes, 0, kNoAllocRows * sizeof(unsigned), ctx->stream));
+    HY3A_CUDA(ctx, cudaMemsetAsync(scratch + kNoAllocRecordBytes, 0, 2 * kNoAllocRows * sizeof(unsigned), ctx->stream));
     decode_args a;
     memset(&a, 0, sizeof(a));
     a.q = q; a.q_stride = q_stride; a.out = out; a.out_stride = out_stride;
     a.scratch = reinterpret_cast<float *>(scratch);
     a.counters = reinterpret_cast<unsigned *>(scratch + kNoAllocRecordBytes);
+    a.n_counters = kNoAllocRows;
     a.err = ctx->d_err; a.layer = layer; a.trace = ctx->d_trace;
     a.early_prefetch = 0;
     hy3a_cache_view cv = hy3a_view(ctx);

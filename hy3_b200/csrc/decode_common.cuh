@@ -28,9 +28,11 @@ struct hy3a_decode_args {
     int n_dest, my_rank;
     uint4 *dest[8];
     const uint4 *gathered;        /* local: [n_dest][n*kv_heads*8][65] lines of the slot */
-    unsigned *shard_round;        /* local: [n*kv_heads] uses of the slot so far */
-    float *scratch;       /* [(gridDim.x + n*kv_heads)][8][130] */
-    unsigned int *counters;
+    unsigned *shard_round;        /* local: [n*kv_heads*8] uses of the slot so far, per head */
+    float *scratch;       /* merge records: [(gridDim.x + n*kv_heads)][8][HY3A_REC_FLOATS] */
+    unsigned int *counters; /* [2][n_counters]: arrivals per (row, KV head) segment, then finished folds */
+    int n_counters;
+    int spread;           /* CTA-aligned segments may spread their fold over several CTAs (the whole grid is resident) */
     unsigned int *err;
     int layer;
     /* fused step (fused != 0): the kernel itself normalises + rotates the queries read from q_in and
@@ -158,6 +160,24 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     if (atomicCAS(err, 0u, 1u) == 0u) err[1] = where;
     return false;
 }
+/* ---- pieces both decode kernels use */
+__device__ __forceinline__ void imma16832(int c[4], const uint4 &a, unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float2 unpack_h2(unsigned v) {
+    __half2 h = *reinterpret_cast<__half2 *>(&v);
+    return __half22float2(h);
+}
+/* INT8/INT4 caches, Q.K^T on m16n8k32: for k-step kk (0..3) the eight k-slots (4tig..4tig+3, 16+4tig..16+4tig+3) of
+ * thread-in-group tig carry head dims kdim32<DT>(kk, tig, 0..7): exactly the dims whose codes the thread gets out of its own
+ * 16-byte loads of a K row. */
+template <int DT> __device__ __forceinline__ int kdim32(int kk, int tig, int s) {
+    if (DT == 1) return 16 * (tig + 4 * (s >> 2)) + 4 * kk + (s & 3);   /* chunk tig / tig+4, word kk */
+    return 32 * tig + 8 * kk + 2 * (s & 3) + (s >> 2);                   /* word kk: even nibbles, then odd nibbles */
+}
+
 /* Sequence sharding: lines of one head's record in a gather buffer: line 0 = {m, l}, line 1 + j = acc[2j], acc[2j+1]. */
 constexpr int kShardLines = HY3A_PARTIAL_FLOATS / 2;   /* 65 */
 __device__ __forceinline__ void shard_store_line(uint4 *p, float x, float y, unsigned flag) {

@@ -164,7 +164,7 @@ int hy3a_decode_step(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_strid
  * never calls cudaMalloc, cudaFree or any allocating routine.  Same arguments and results as
  * hy3a_decode without `partials`.
  * Limits: at most 64 (batch row, owned KV head) pairs per call, i.e. 8 rows with all 8 KV heads;
- * larger batches are refused with HY3A_EINVAL.  The array (2.6 MB) is held by every GPU that
+ * larger batches are refused with HY3A_EINVAL.  The array (2.4 MB) is held by every GPU that
  * loads the library until the process exits.  The first call on a device looks the array's
  * device address up (cudaGetSymbolAddress) -- make that first call outside any stream capture.
  * All contexts on a device share the array, and it keeps the last call's contents (the counters

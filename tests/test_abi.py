@@ -1,5 +1,6 @@
-"""The drop-in boundary: every symbol include/*.h declares is exported by the built library
-and bound by the ctypes table; no compute is called (runs without a GPU)."""
+"""The drop-in boundary: every symbol include/*.h declares is exported by the built libraries -- the attention-level
+ABI (hy3_attn.h, libhy3attn.so, bound by the ctypes table) and the reference engine's own backend API (hy3_gpu_dropin.h,
+libhy3_gpu.so: hy3_gpu_init / hy3_gpu_free / hy3_eval_gpu); no compute is called (runs without a GPU)."""
 import ctypes as C
 import os
 import re
@@ -31,6 +32,26 @@ def test_attn_header_symbols_exported_and_bound(lib):
     for s in syms:
         assert hasattr(lib, s), "library does not export %s" % s
     assert sorted(PROTOTYPES) == syms, "ctypes table and header disagree"
+
+
+def test_engine_api_symbols_exported():
+    """The three symbols the reference engine binds (hy3_gpu.h:6-8, hy3.h:79) and what the library expects from the
+    engine in return (hy3.h:74, :84-85), read from the dynamic symbol table."""
+    import subprocess
+    from hy3_b200 import _build
+    if not os.path.exists(_build.DROPIN_LIB):
+        if _build.reference_dir() is None:
+            pytest.skip("libhy3_gpu.so is not built and the reference checkout is not here to build it")
+        _build.build()
+    out = subprocess.run(["nm", "-D", _build.DROPIN_LIB], capture_output=True, text=True, check=True).stdout
+    defined = {ln.split()[-1] for ln in out.splitlines() if " T " in ln}
+    undefined = {ln.split()[-1] for ln in out.splitlines() if ln.strip().startswith("U ")}
+    syms = declared_symbols("hy3_gpu_dropin.h")
+    assert {"hy3_gpu_init", "hy3_gpu_free", "hy3_eval_gpu"} <= set(syms)
+    for s in syms:
+        assert s in defined, "libhy3_gpu.so does not export %s" % s
+    assert {"hy3_rope_get_params", "forward_layer_dense", "forward_layer_moe"} <= undefined
+    assert {s for s in declared_symbols("hy3_attn.h")} <= defined       # the attention ABI is part of the same object set
 
 
 def test_config_struct_layout(lib):

@@ -129,6 +129,23 @@ def test_committed_gpu_fixture(cuda, oracle):
         assert np.array_equal(vs, g["vslots_" + dt])
         assert np.array_equal(make_slots(oracle, v, dt), g["vslots_" + dt])
         assert np.array_equal(make_slots(oracle, k, dt), g["kslots_" + dt])
+    # the reference's own fused norm + RoPE kernel (hy3_gpu.cu:144-164), run on a B200 when the fixture was made, on the
+    # same seeded inputs: the queries must agree bit for bit; K rows take the query path with the K weights for the same check
+    q1 = oracle.fill_normal((1, 64, 128), SEED, 1)
+    k1 = oracle.fill_normal((1, 8, 128), SEED, 2)
+    w2 = (1.0 + 0.02 * oracle.fill_normal((2, 128), SEED, 3)).astype(np.float32)
+    inv, af = oracle.rope_table()
+    inv4, af4 = oracle.rope_table(yarn=1, factor=4.0)
+    cases = {"p0": ((inv, af), 0, (1, 0, 0)), "p4096": ((inv, af), 4096, (1, 0, 0)),
+             "yarn4_p1048575": ((inv4, af4), 1048575, (1, 0, 0)), "stride7_p300": ((inv, af), 300, (7, 0, 0)),
+             "jump_p50": ((inv, af), 50, (1, 300000, 40))}
+    for name, (table, pos, probes) in cases.items():
+        qo, _, _, _ = run_append(cuda, oracle, "int8", 1e-5, q1, k1, k1, w2[0], w2[1], [pos], table=table, probes=probes)
+        assert np.array_equal(qo[0], g["gpu_normrope_%s_q" % name]), "%s: queries differ from the reference CUDA kernel" % name
+        qk = np.zeros((1, 64, 128), np.float32)
+        qk[0, :8] = k1[0]
+        ko, _, _, _ = run_append(cuda, oracle, "int8", 1e-5, qk, k1, k1, w2[1], w2[1], [pos], table=table, probes=probes)
+        assert np.array_equal(ko[0, :8], g["gpu_normrope_%s_k" % name]), "%s: keys differ from the reference CUDA kernel" % name
 
 
 @pytest.mark.parametrize("heads", [(0, 8), (4, 4)])

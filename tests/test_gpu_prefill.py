@@ -115,3 +115,29 @@ def test_prefill_chunks_reuse_converted_pages(cuda, oracle, dt, monkeypatch):
     want = oracle.prefill_causal(qf, Kf, Vf, base, rows=[0, n - 1])
     for i in (0, n - 1):
         check_attention(out[i], want[i], "%s before cut: base=%d row %d" % (dt, base, i))
+
+
+@pytest.mark.parametrize("dt", ["fp16", "int8"])
+def test_append_twice_refreshes_operands(cuda, oracle, dt):
+    """The same batch appended a second time with other K/V (no new hy3a_batch_set in between): the chunk attention
+    must see the second version, i.e. the kept fp16 operands of the layer may not go stale."""
+    import torch
+    from hy3_b200 import Hy3Attn
+    n = 200
+    ctx = Hy3Attn(kv_dtype=dt, n_layers=1, max_batch=n, max_tokens=512)
+    q = oracle.fill_normal((n, 64, 128), SEED, 901)
+    kv = [(oracle.fill_normal((n, 8, 128), SEED, 902 + 2 * i), oracle.fill_normal((n, 8, 128), SEED, 903 + 2 * i)) for i in range(2)]
+    tq = torch.from_numpy(q).to(cuda)
+    q16 = torch.empty((n, 64, 128), dtype=torch.float16, device=cuda)
+    ctx.batch_set([0] * n, list(range(n)))
+    for k, v in kv:
+        ctx.append(0, tq, torch.from_numpy(k).to(cuda), torch.from_numpy(v).to(cuda), q_out=False, q_out16=q16)
+        out = ctx.prefill(0, 0, 0, q16)
+    ctx.sync()
+    ks, vs = ctx.export_kv(0, 0, 0, n)
+    rows = [0, 1, 100, n - 1]
+    want = oracle.prefill_causal(q16.float().cpu().numpy(), slots_to_float(oracle, ks, dt), slots_to_float(oracle, vs, dt), 0, rows=rows)
+    out = out.cpu().numpy()
+    for i in rows:
+        check_attention(out[i], want[i], "%s second append, row %d" % (dt, i))
+    ctx.close()
