@@ -20,7 +20,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhy3attn.so")
 DROPIN_LIB = os.path.join(HERE, "libhy3_gpu.so")
-SOURCES = ["append.cu", "decode.cu", "prefill.cu", "capi.cu", "selftest.cu"]
+SOURCES = ["append.cu", "decode.cu", "decode_umma.cu", "prefill.cu", "capi.cu", "selftest.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC,-fvisibility=default", "-I", os.path.join(ROOT, "include")]
 

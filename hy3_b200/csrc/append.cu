@@ -280,11 +280,11 @@ __global__ void hy3a_xport_kernel(hy3a_cache_view cache, int layer, int seq, int
     if (DT == 0) { int off = is_v ? g.v_off + hy3a_v16_dim_off(tok, d0) : hy3a_k_dim_off<0>(tok, d0); for (int b = 0; b < 8; b++) pp[b] = page + off + b; }
     else if (DT == 1) {
         if (!is_v) { int off = hy3a_k_dim_off<1>(tok, d0); for (int b = 0; b < 4; b++) pp[b] = page + off + b; }
-        else { int o0 = g.v_off + hy3a_v_unit_off<1>(tok, d0), o1 = g.v_off + hy3a_v_unit_off<1>(tok, d0 + 2); pp[0] = page + o0; pp[1] = page + o0 + 1; pp[2] = page + o1; pp[3] = page + o1 + 1; }
+        else { for (int b = 0; b < 4; b++) pp[b] = page + g.v_off + hy3a_vt_off(d0 + b, tok); }
     } else {
         int off = is_v ? g.v_off + hy3a_v_unit_off<2>(tok, d0) : hy3a_k_dim_off<2>(tok, d0); pp[0] = page + off; pp[1] = page + off + 1;
     }
-    const uint8_t flip = (is_v && DT != 0) ? (DT == 1 ? 0x80 : 0x88) : 0x00;   /* V codes are stored offset-binary */
+    const uint8_t flip = (is_v && DT == 2) ? 0x88 : 0x00;   /* INT4 V nibbles are stored offset-binary */
     for (int b = 0; b < sbytes; b++) { if (import) *pp[b] = sp[b] ^ flip; else sp[b] = *pp[b] ^ flip; }
     if (DT != 0 && q4 == 0) {
         uint8_t *sc = page + (is_v ? g.vs_off : g.ks_off) + tok * 2;
@@ -296,7 +296,7 @@ __global__ void hy3a_xport_kernel(hy3a_cache_view cache, int layer, int seq, int
 }
 
 /* Reset pages to the "all codes zero" state: zero bytes everywhere except the V code area of
- * INT8/INT4 pages, whose offset-binary zero is 0x80 / 0x88.  grid = pages, block 256.       */
+ * INT4 pages, whose offset-binary zero is 0x88.  grid = pages, block 256.       */
 __global__ void hy3a_init_pages_kernel(uint8_t *pool, size_t first_page, int page_bytes, int v_off, int v_end, unsigned flip_word) {
     uint4 *page = reinterpret_cast<uint4 *>(pool + (first_page + blockIdx.x) * (size_t)page_bytes);
     const int lo = v_off / 16, hi = v_end / 16;
@@ -310,7 +310,7 @@ __global__ void hy3a_init_pages_kernel(uint8_t *pool, size_t first_page, int pag
 
 int hy3a_launch_init_pages(hy3a_ctx *ctx, size_t first_page, size_t n_pages) {
     const hy3a_geom g = ctx->geom;
-    const unsigned flip = g.dtype == 1 ? 0x80808080u : (g.dtype == 2 ? 0x88888888u : 0u);
+    const unsigned flip = g.dtype == 2 ? 0x88888888u : 0u;
     const int v_end = g.dtype == 0 ? g.page_bytes : g.ks_off;
     for (size_t done = 0; done < n_pages;) {
         size_t chunk = n_pages - done > 1048576 ? 1048576 : n_pages - done;

@@ -12,6 +12,9 @@
 #ifndef HY3A_DECODE_WARPS
 #define HY3A_DECODE_WARPS 11
 #endif
+#ifndef HY3A_UMMA_STAGES
+#define HY3A_UMMA_STAGES 6    /* pages in the shared-memory ring of the INT8 decode kernel */
+#endif
 #define HY3A_ERR_WORDS 4
 #define HY3A_REC_FLOATS 132   /* a head's {m, l, acc[128]} record in the merge scratch, padded to a multiple of 16 bytes */
 #define HY3A_RING_SLOTS 16

@@ -466,6 +466,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             unsigned it = 0;
             bool ok = true;
             bool waited = false;   /* griddepcontrol.wait executed yet? */
+            const unsigned long long pol = l2_evict_first_policy();
             if (!a.early_prefetch) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
             for (long long u = u_begin; u < u_end && ok;) {
                 segment sg = locate(s_prefix, batch, n, G, u, u_end);
@@ -482,7 +483,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     if (!ok) break;
                     const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, sg.hl) * (size_t)cache.page_bytes;
                     mbar_expect_tx(bar_base + 8 * stage, (unsigned)geom.page_bytes);
-                    bulk_g2s(ring_base + stage * (unsigned)geom.page_bytes, page, (unsigned)geom.page_bytes, bar_base + 8 * stage);
+                    bulk_g2s(ring_base + stage * (unsigned)geom.page_bytes, page, (unsigned)geom.page_bytes, bar_base + 8 * stage, pol);
                     TRACE(32 + it);
                 }
                 u = sg.seg_u0 + sg.p_end;
@@ -998,11 +999,13 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
     memset(&a, 0, sizeof(a));
     a.q = q; a.q_stride = q_stride; a.out = out; a.out_stride = out_stride; a.user_partials = partials;
     a.scratch = ctx->d_partials; a.counters = ctx->d_counters; a.n_counters = ctx->cfg.max_batch * ctx->cfg.kv_head_count; a.err = ctx->d_err; a.layer = layer;
-    /* the spread fold pays off where the epilogue is the cross-GPU exchange (8 CTAs store to the peers instead of one);
-     * its folders wait for the other pieces, so every CTA of the grid must be resident */
+    /* the spread fold pays off where the epilogue is the cross-GPU exchange (8 CTAs store to the peers instead of one); on one
+     * GPU the folders only hold their SMs longer, which delays the next launch's CTAs there.  Its folders wait for the other
+     * pieces, so every CTA of the grid must be resident */
     a.spread = ctx->shard_slot >= 0 && ctx->decode_ctas <= ctx->sm_count;
     a.trace = ctx->d_trace;
     a.early_prefetch = ctx->use_pdl && !ctx->bulk_write_pending;
+    { static int l2p = -1; if (l2p < 0) { const char *e = getenv("HY3A_L2_PREFETCH"); l2p = e ? atoi(e) : 1; } a.l2_prefetch = l2p; }
     if (ctx->shard_slot >= 0) {   /* set by hy3a_decode_step_sharded around this call */
         const int W = ctx->shard_world, slot = ctx->shard_slot;
         const size_t n_seg = (size_t)ctx->shard_rows * ctx->cfg.kv_head_count;
@@ -1024,7 +1027,7 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
     cudaError_t e;
     switch (ctx->geom.dtype) {
         case 0: e = launch_decode_dt<0>(ctx, cv, bv, a); break;
-        case 1: e = launch_decode_dt<1>(ctx, cv, bv, a); break;
+        case 1: e = hy3a_launch_decode_umma(ctx, cv, bv, a); break;
         default: e = launch_decode_dt<2>(ctx, cv, bv, a); break;
     }
     ctx->launches++;
@@ -1085,7 +1088,7 @@ extern "C" int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, siz
     cudaError_t e;
     switch (ctx->geom.dtype) {
         case 0: e = launch_decode_dt<0>(ctx, cv, bv, a); break;
-        case 1: e = launch_decode_dt<1>(ctx, cv, bv, a); break;
+        case 1: e = hy3a_launch_decode_umma(ctx, cv, bv, a); break;
         default: e = launch_decode_dt<2>(ctx, cv, bv, a); break;
     }
     ctx->launches++;

@@ -39,6 +39,7 @@ struct hy3a_decode_args {
      * the CTA that streams the page of the newest slot quantises and appends the new K / V row   */
     int fused;
     int early_prefetch;   /* pages below the newest slots may be fetched before griddepcontrol.wait */
+    int l2_prefetch;      /* ask L2 for the pages beyond the ring as soon as the preceding kernel is complete */
     const float *q_in, *k_in, *v_in;
     size_t qi_stride, ki_stride, vi_stride;
     float *q_out;         /* optional: normalised + rotated queries, fp32 [n][64][128] */
@@ -49,6 +50,9 @@ struct hy3a_decode_args {
     int stages;           /* staged variant: pages in the shared-memory ring (2..8) */
     int prefix_bytes;     /* bytes reserved for the page-count prefix */
 };
+
+/* the INT8 decode kernel (decode_umma.cu) */
+cudaError_t hy3a_launch_decode_umma(hy3a_ctx *ctx, const hy3a_cache_view &cv, const hy3a_batch_view &bv, hy3a_decode_args &a);
 
 namespace {
 
@@ -88,7 +92,7 @@ __device__ __forceinline__ segment locate(const int *s_prefix, const hy3a_batch_
     sg.row = lo;
     sg.pages = s_prefix[lo + 1] - s_prefix[lo];
     const long long row_u0 = (long long)G * s_prefix[lo];
-    sg.hl = (int)((u - row_u0) / sg.pages);
+    sg.hl = (int)((unsigned)(u - row_u0) / (unsigned)sg.pages);   /* both fit 32 bits: a 64-bit division costs hundreds of cycles */
     sg.seg_u0 = row_u0 + (long long)sg.hl * sg.pages;
     sg.seg_u1 = sg.seg_u0 + sg.pages;
     sg.p_begin = (int)(u - sg.seg_u0);
@@ -143,8 +147,16 @@ __device__ __forceinline__ bool mbar_wait_blocking(unsigned bar, unsigned parity
     if (atomicCAS(err, 0u, 1u) == 0u) { err[1] = where; err[2] = blockIdx.x; err[3] = bar; }
     return false;
 }
-__device__ __forceinline__ void bulk_g2s(unsigned dst, const void *src, unsigned bytes, unsigned bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+/* The KV stream is read once per step: its lines are marked evict-first in L2, so that what is small and re-read by every
+ * launch (queries, batch descriptor, block table, norm weights, merge records) stays resident beside 68 MB of pages per launch. */
+__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void *src, unsigned bytes, unsigned bar, unsigned long long policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
 }
 /* Bounded wait: gives up after ~2^22 polls (far beyond any legitimate wait), records the
  * failure in the device error word and raises the CTA-wide abort flag; once the flag is up

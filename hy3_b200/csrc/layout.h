@@ -8,7 +8,7 @@
  *
  *      [ K codes : 128 rows ][ V codes : 64 pair-rows (128 rows for FP16) ][ K scales fp16[128] ][ V scales fp16[128] ]
  *
- *   INT8  33 280 B   K row 128 B,  V pair-row 256 B
+ *   INT8  33 280 B   K row 128 B,  V area = the TRANSPOSED tile: 128 rows (head dims) x 128 token bytes
  *   INT4  16 896 B   K row  64 B,  V pair-row 128 B
  *   FP16  65 536 B   K row 256 B,  V row      256 B, no scales
  *
@@ -17,7 +17,11 @@
  * Sequences map token/128 -> block through a block table, so growth, rollback and
  * ragged batches never move data.
  *
- * V "pair layout" (INT8/INT4): tokens 2i and 2i+1 share a pair-row in which 16-bit units
+ * INT8 V area: row = head dim, column = token, two's complement, in the tensor core's K-major 128-byte-swizzle order
+ * (16-byte chunk c of row r sits at chunk c ^ (r & 7)), so that the page copied verbatim into 1024-byte-aligned shared
+ * memory is a tcgen05.mma operand with the head dims as M and the tokens as K (decode_umma.cu).
+ *
+ * V "pair layout" (INT4): tokens 2i and 2i+1 share a pair-row in which 16-bit units
  * alternate between the two tokens (unit u of token 2i+e sits at 16-bit index 2u+e).  A
  * 32-bit word then holds the same dims of two consecutive tokens, which is exactly the
  * operand pairing the P.V tensor-core fragment wants, so the int->fp16 conversion and the
@@ -71,7 +75,11 @@ template <int DT> HY3A_HD int hy3a_k_dim_off(int tok, int d) {
     return hy3a_k_chunk_off<0>(tok, d >> 3) + ((d & 7) << 1);                 /* 2 B / dim */
 }
 
-/* ---- V (INT8 / INT4 pair layout): offset relative to the V area of chunk `chunk` of pair-row pr. */
+/* ---- V, INT8: byte offset relative to the V area of (head dim d, token tok) in the transposed, swizzled tile. */
+HY3A_HD int hy3a_vt_off(int d, int tok) { return d * 128 + ((((tok >> 4) ^ (d & 7))) << 4) + (tok & 15); }
+
+/* ---- V (INT4 pair layout; DT = 1 is the geometry the fp16-converting decode path of INT8 used and is kept for the
+ * template's sake): offset relative to the V area of chunk `chunk` of pair-row pr. */
 template <int DT> HY3A_HD int hy3a_v_chunk_off(int pr, int chunk) {
     const int prow = (DT == 1) ? 256 : 128;
     return pr * prow + ((chunk ^ ((pr & 3) << 1)) << 4);

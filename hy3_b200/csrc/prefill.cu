@@ -178,8 +178,7 @@ __global__ void __launch_bounds__(256) hy3a_kv_to_f16_kernel(hy3a_cache_view cac
                 if (DT == 0) {
                     v = __half2float(*reinterpret_cast<const __half *>(page + g.v_off + hy3a_v16_dim_off(tok, d)));
                 } else if (DT == 1) {
-                    const int b = page[g.v_off + hy3a_v_unit_off<1>(tok, d & ~1) + (d & 1)];
-                    v = (float)(b - 128) * __half2float(vs[tok]);
+                    v = (float)(signed char)page[g.v_off + hy3a_vt_off(d, tok)] * __half2float(vs[tok]);
                 } else {
                     const int b = page[g.v_off + hy3a_v_unit_off<2>(tok, d & ~3) + ((d & 3) >> 1)];
                     v = (float)(((b >> ((d & 1) * 4)) & 0xF) - 8) * __half2float(vs[tok]);

@@ -57,16 +57,13 @@ __device__ __forceinline__ unsigned store_row(uint8_t *page, const hy3a_geom &g,
             unsigned w = (unsigned)(c[0] & 0xFF) | ((unsigned)(c[1] & 0xFF) << 8) | ((unsigned)(c[2] & 0xFF) << 16) | ((unsigned)(c[3] & 0xFF) << 24);
             *reinterpret_cast<unsigned *>(page + hy3a_k_dim_off<1>(tok, d0)) = w;
         } else {
-            /* V codes are kept offset-binary (c + 128): the decode kernel's byte-permute conversion
-             * to fp16 then needs no sign fix-up; export converts back to two's complement          */
-            unsigned short u0 = (unsigned short)((((c[0] & 0xFF) | ((c[1] & 0xFF) << 8))) ^ 0x8080);
-            unsigned short u1 = (unsigned short)((((c[2] & 0xFF) | ((c[3] & 0xFF) << 8))) ^ 0x8080);
-            *reinterpret_cast<unsigned short *>(page + g.v_off + hy3a_v_unit_off<1>(tok, d0)) = u0;
-            *reinterpret_cast<unsigned short *>(page + g.v_off + hy3a_v_unit_off<1>(tok, d0 + 2)) = u1;
+            /* V codes go into the transposed tile: one byte per (head dim, token) */
+#pragma unroll
+            for (int j = 0; j < 4; j++) page[g.v_off + hy3a_vt_off(d0 + j, tok)] = (uint8_t)(c[j] & 0xFF);
         }
     } else {
         unsigned short u = (unsigned short)((c[0] & 0xF) | ((c[1] & 0xF) << 4) | ((c[2] & 0xF) << 8) | ((c[3] & 0xF) << 12));
-        if (is_v) u ^= 0x8888;   /* V nibbles offset-binary (n + 8), as for INT8 */
+        if (is_v) u ^= 0x8888;   /* V nibbles offset-binary (n + 8): the decode kernel's nibble -> fp16 conversion then needs no sign fix-up */
         int off = is_v ? g.v_off + hy3a_v_unit_off<2>(tok, d0) : hy3a_k_dim_off<2>(tok, d0);
         *reinterpret_cast<unsigned short *>(page + off) = u;
     }
