@@ -338,6 +338,8 @@ int hy3a_launch_append(hy3a_ctx *ctx, int layer, const float *q_in, size_t q_str
         if (ctx->batch_seq_uniform) hy3a_mirror_truncate(ctx, ctx->batch_seq0, layer, lowest);
         else { ctx->pf_mntok[layer] = 0; }
     }
+    if (k_in && ctx->pf_mseq < 0 && ctx->pf_mk[layer] && ctx->batch_contig && ctx->batch_slot0 == 0)
+        ctx->pf_mseq = ctx->batch_seq0;     /* mirrors allocated at create belong to the first sequence that is ingested from slot 0 */
     if (k_in && ctx->pf_mk[layer] && ctx->batch_contig && ctx->batch_seq0 == ctx->pf_mseq && ctx->batch_slot0 == ctx->pf_mntok[layer] &&
         ctx->batch_slot0 + ctx->batch_n <= ctx->pf_mcap[layer]) {
         a.mirror_k = (__half *)ctx->pf_mk[layer]; a.mirror_v = (__half *)ctx->pf_mv[layer]; a.mirror_stride = ctx->pf_mcap[layer];

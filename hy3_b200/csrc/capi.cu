@@ -202,6 +202,30 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     CREATE_CUDA(cudaMemsetAsync(ctx->d_trace, 0, (size_t)512 * 64 * sizeof(unsigned long long), ctx->stream));
     CREATE_CUDA(cudaMalloc(&ctx->d_err, HY3A_ERR_WORDS * sizeof(unsigned)));
     CREATE_CUDA(cudaMemsetAsync(ctx->d_err, 0, HY3A_ERR_WORDS * sizeof(unsigned), ctx->stream));
+    /* operand mirrors of the chunked prefill, sized for a whole sequence, when a context that takes chunks (max_batch >= 16:
+     * one query tile) can hold all layers' mirrors within the budget: hy3a_prefill then never allocates.  Zeroed once:
+     * columns past a sequence's end are read by the last tile (and masked), so they must never hold a NaN or Inf pattern. */
+    if (ctx->pf_mbudget && cfg->max_batch >= 16) {
+        const int seq_cap = (cfg->max_blocks_per_seq * HY3A_PT + 1023) / 1024 * 1024;
+        const size_t per_layer = 2 * (size_t)cfg->kv_head_count * seq_cap * HY3A_D * 2 /* fp16 */;
+        if (per_layer * (size_t)cfg->n_layers <= ctx->pf_mbudget) {
+            bool ok = true;
+            for (int l = 0; l < cfg->n_layers && ok; l++) {
+                ok = cudaMalloc(&ctx->pf_mk[l], per_layer / 2) == cudaSuccess && cudaMalloc(&ctx->pf_mv[l], per_layer / 2) == cudaSuccess &&
+                     cudaMemsetAsync(ctx->pf_mk[l], 0, per_layer / 2, ctx->stream) == cudaSuccess &&
+                     cudaMemsetAsync(ctx->pf_mv[l], 0, per_layer / 2, ctx->stream) == cudaSuccess;
+                if (ok) { ctx->pf_mcap[l] = seq_cap; ctx->pf_mbytes += per_layer; }
+            }
+            if (!ok) {   /* no room beside the pool: the mirrors are then grown on demand, or the shared workspace is used */
+                cudaGetLastError();
+                for (int l = 0; l < cfg->n_layers; l++) {
+                    cudaFree(ctx->pf_mk[l]); cudaFree(ctx->pf_mv[l]);
+                    ctx->pf_mk[l] = ctx->pf_mv[l] = NULL; ctx->pf_mcap[l] = 0;
+                }
+                ctx->pf_mbytes = 0;
+            }
+        }
+    }
     CREATE_CUDA(cudaHostAlloc((void **)&ctx->h_err, HY3A_ERR_WORDS * sizeof(unsigned), cudaHostAllocDefault));
 
     ctx->ring_slot_bytes = (size_t)3 * cfg->max_batch * sizeof(int);

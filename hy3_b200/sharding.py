@@ -12,9 +12,21 @@ Two partitions of the attention path, neither present in the single-GPU referenc
 
 The compute callables are injected so that the exchange logic can run on CPU ranks (gloo) in tests.
 """
+import datetime
+
 import numpy as np
 
 PARTIAL_FLOATS = 130
+ETIMEOUT = -6       # HY3A_ETIMEOUT of include/hy3_attn.h: the status a bounded wait returns when it runs out
+
+
+class ExchangeError(RuntimeError):
+    """The all-gather of a layer's records did not complete (a rank never joined, left, or the collective failed).
+    `status` is the library's time-out status; the local records of the step are intact."""
+
+    def __init__(self, status, message):
+        RuntimeError.__init__(self, message)
+        self.status = status
 
 
 def kv_head_range(rank, world, n_kv_heads=8):
@@ -44,12 +56,17 @@ class SequenceShardedDecode:
     stream while layer l+1 streams its KV: `partial(layer, q, slot)` then, later,
     `exchange_merge(slot, out)`; `n_slots` buffer sets let that many exchanges be in flight."""
 
-    def __init__(self, partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty_like, n_slots=1):
+    def __init__(self, partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty_like, n_slots=1, timeout_s=None):
         """partial_fn(layer, q, partial_buf): fill [n_rows, n_heads, 130] for the local token range;
         merge_fn(gathered, n_parts, out): fold [world, n_rows, n_heads, 130] in rank order;
-        all_gather_fn(gathered, local): the collective; empty_like(shape): buffer factory."""
+        all_gather_fn(gathered, local): the collective -- it may return a work handle (wait(timeout) -> bool);
+        empty_like(shape): buffer factory.
+        timeout_s: how long exchange_merge waits for the other ranks before it raises ExchangeError (None: the
+        collective's own time-out applies; the reference has no multi-rank path and exits on any CUDA error,
+        hy3_gpu.cu:17-20)."""
         self.partial_fn, self.merge_fn, self.all_gather_fn = partial_fn, merge_fn, all_gather_fn
         self.world, self.n_rows, self.n_heads = world, n_rows, n_heads
+        self.timeout_s = timeout_s
         self.local = [empty_like((n_rows, n_heads, PARTIAL_FLOATS)) for _ in range(n_slots)]
         self.gathered = [empty_like((world, n_rows, n_heads, PARTIAL_FLOATS)) for _ in range(n_slots)]
 
@@ -57,20 +74,37 @@ class SequenceShardedDecode:
         self.partial_fn(layer, q, self.local[slot])
 
     def exchange_merge(self, slot, out):
+        """All-gather of the slot's records and the fold.  Raises ExchangeError (status ETIMEOUT) when the other ranks do
+        not deliver within timeout_s; `out` is then untouched and the object stays usable: detach() continues on this
+        rank's tokens alone."""
         if self.world == 1:
             self.merge_fn(self.local[slot], 1, out)
-        else:
-            self.all_gather_fn(self.gathered[slot], self.local[slot])
-            self.merge_fn(self.gathered[slot], self.world, out)
+            return out
+        try:
+            work = self.all_gather_fn(self.gathered[slot], self.local[slot])
+            if work is not None and hasattr(work, "wait"):
+                done = work.wait(datetime.timedelta(seconds=self.timeout_s)) if self.timeout_s is not None else work.wait()
+                if done is False:
+                    raise ExchangeError(ETIMEOUT, "exchange_merge: the all-gather did not complete within %.1f s" % self.timeout_s)
+        except ExchangeError:
+            raise
+        except RuntimeError as e:       # torch.distributed reports a timed-out or broken collective as RuntimeError
+            raise ExchangeError(ETIMEOUT, "exchange_merge: the all-gather failed or timed out (%s)" % str(e).splitlines()[0]) from e
+        self.merge_fn(self.gathered[slot], self.world, out)
         return out
+
+    def detach(self):
+        """Continue without the other ranks (after an ExchangeError): the fold then covers this rank's records only."""
+        self.world = 1
 
     def step(self, layer, q, out):
         self.partial(layer, q, 0)
         return self.exchange_merge(0, out)
 
 
-def make_cuda_sharded_decode(ctx, n_rows, group=None, n_slots=1):
-    """Wire SequenceShardedDecode to a Hy3Attn context and torch.distributed (NCCL)."""
+def make_cuda_sharded_decode(ctx, n_rows, group=None, n_slots=1, timeout_s=None):
+    """Wire SequenceShardedDecode to a Hy3Attn context and torch.distributed (NCCL).  With timeout_s the all-gather is
+    issued as an asynchronous work item and waited for on the host for at most that long."""
     import torch
     import torch.distributed as dist
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -87,12 +121,15 @@ def make_cuda_sharded_decode(ctx, n_rows, group=None, n_slots=1):
         ctx.merge_partials(gathered, n_parts, n_rows, n_heads, out)
 
     def all_gather_fn(gathered, local):
-        dist.all_gather_into_tensor(gathered, local, group=group)
+        if timeout_s is None:
+            dist.all_gather_into_tensor(gathered, local, group=group)      # stream-ordered, no host wait (graph capture safe)
+            return None
+        return dist.all_gather_into_tensor(gathered, local, group=group, async_op=True)
 
     def empty(shape):
         return torch.empty(shape, dtype=torch.float32, device=dev)
 
-    return SequenceShardedDecode(partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty, n_slots)
+    return SequenceShardedDecode(partial_fn, merge_fn, all_gather_fn, world, n_rows, n_heads, empty, n_slots, timeout_s)
 
 
 def merge_partials_numpy(gathered):

@@ -251,6 +251,11 @@ class _RefCpu:
     def max_threads(self):
         return int(self.lib.hy3ref_max_threads())
 
+    def set_threads(self, n):
+        """OpenMP team size of the *_mt entry points; returns the size in effect."""
+        self.lib.hy3ref_set_threads.restype = C.c_int
+        return int(self.lib.hy3ref_set_threads(C.c_int(int(n))))
+
 
 class _RefGpu:
     """The reference's own CUDA kernels (hy3_gpu.cu) from oracle/_ref/; needs a GPU to call."""

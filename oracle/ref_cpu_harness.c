@@ -110,3 +110,15 @@ int hy3ref_max_threads(void) {
     return 1;
 #endif
 }
+
+/* Sets the OpenMP team size the *_mt entry points use (the benchmark's reference arm passes the host's core count, so
+ * the team does not depend on OMP_NUM_THREADS of the launching shell); returns the size in effect. */
+int hy3ref_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}

@@ -100,3 +100,89 @@ def test_ranges():
             assert all(a[0] % 128 == 0 for a in rs if a[1] > a[0])      # non-empty shards start on page boundaries
             sizes = [(b - a + 127) // 128 for a, b in rs]
             assert max(sizes) - min(sizes) <= 1
+
+
+# ------------------------------------------------------------------ failure path: a rank that never enters the exchange
+EXCHANGE_TIMEOUT_S = 3.0
+
+
+def _failing_worker(rank, world, port, ntok, q, K, V, ret):
+    """Rank 1 computes nothing and never enters the all-gather (it sleeps past the time-out and leaves); rank 0 must get
+    an error status from exchange_merge within the stated time-out, not hang, and decode correctly afterwards alone."""
+    sys.path.insert(0, ROOT)
+    import time
+    import torch
+    import torch.distributed as dist
+    import oracle
+    from hy3_b200.sharding import SequenceShardedDecode, ExchangeError, ETIMEOUT, sequence_range, merge_partials_numpy
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    if rank != 0:
+        time.sleep(EXCHANGE_TIMEOUT_S + 4.0)          # between steps: nothing of this rank is in flight
+        os._exit(0)
+    t0, t1 = sequence_range(rank, world, ntok)
+    n_rows = q.shape[0]
+
+    def partial_fn(layer, qq, buf):
+        for r in range(n_rows):
+            buf[r] = torch.from_numpy(oracle.attention_partial(qq[r], K, V, t0, t1))
+
+    def all_gather_fn(gathered, local):
+        parts = [torch.empty_like(local) for _ in range(world)]
+        work = dist.all_gather(parts, local, async_op=True)
+
+        class Handle:
+            def wait(self, timeout=None):
+                ok = work.wait(timeout) if timeout is not None else work.wait()
+                for i, p in enumerate(parts):
+                    gathered[i] = p
+                return ok
+        return Handle()
+
+    def merge_fn(gathered, n_parts, out):
+        g = gathered.numpy() if n_parts > 1 else gathered.numpy()[None]
+        out[:] = torch.from_numpy(merge_partials_numpy(g))
+
+    sd = SequenceShardedDecode(partial_fn, merge_fn, all_gather_fn, world, n_rows, 64,
+                               lambda shape: torch.zeros(shape, dtype=torch.float32), timeout_s=EXCHANGE_TIMEOUT_S)
+    out = torch.full((n_rows, 64, 128), 7.0)
+    sd.partial(0, q, 0)
+    t_start = time.monotonic()
+    status, msg = 0, ""
+    try:
+        sd.exchange_merge(0, out)
+    except ExchangeError as e:
+        status, msg = e.status, str(e)
+    waited = time.monotonic() - t_start
+    untouched = bool((out == 7.0).all())
+    # afterwards: this rank continues on its own tokens
+    sd.detach()
+    sd.step(0, q, out)
+    ret.put((status, status == ETIMEOUT, msg, waited, untouched, out.numpy().copy(), (t0, t1)))
+    ret.close()
+    ret.join_thread()                                 # the queue's feeder thread must have sent the item before the hard exit
+    os._exit(0)                                       # the process group is broken: leave without the collective teardown
+
+
+def test_exchange_times_out_when_a_rank_never_joins(oracle):
+    import torch.multiprocessing as mp
+    ntok, world = 600, 2
+    q = oracle.fill_normal((1, 64, 128), 9, 1)
+    K = oracle.fill_normal((ntok, 8, 128), 9, 2)
+    V = oracle.fill_normal((ntok, 8, 128), 9, 3)
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, ntok, q, K, V, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    status, is_timeout, msg, waited, untouched, out, (t0, t1) = ret.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert status != 0 and is_timeout, "exchange_merge returned no error status: %r" % msg
+    assert waited < EXCHANGE_TIMEOUT_S + 10.0, "exchange_merge took %.1f s" % waited
+    assert untouched, "a failed exchange must not write the output"
+    # rank 0 alone afterwards: attention over its own token range
+    assert np.abs(out[0] - oracle.attention(q[0], K[t0:t1], V[t0:t1])).max() < 2e-6
