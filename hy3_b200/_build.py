@@ -32,13 +32,10 @@ def _newer(src_list, target):
     return any(os.path.getmtime(s) > t for s in src_list)
 
 
-def build(force=False, verbose=False, defines=(), lib_path=None):
-    """defines: extra -D macros (tuning experiments build a second library beside the default one)."""
-    global LIB
+def build(force=False, verbose=False):
     nvcc = os.environ.get("NVCC", "nvcc")
-    tag = "".join("_" + d.replace("=", "") for d in defines)
-    obj_dir = os.path.join(ROOT, "build", "hy3attn" + tag)
-    lib_out = lib_path or (LIB if not defines else os.path.join(HERE, "libhy3attn%s.so" % tag))
+    obj_dir = os.path.join(ROOT, "build", "hy3attn")
+    lib_out = LIB
     os.makedirs(obj_dir, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(ROOT, "include", "hy3_attn.h"))
@@ -48,7 +45,7 @@ def build(force=False, verbose=False, defines=(), lib_path=None):
         obj = os.path.join(obj_dir, s.replace(".cu", ".o"))
         objs.append(obj)
         if force or _newer([src] + headers, obj):
-            cmd = [nvcc] + NVCC_FLAGS + ["-D" + d for d in defines] + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for s, p in procs:
@@ -64,8 +61,7 @@ def build(force=False, verbose=False, defines=(), lib_path=None):
         if r.returncode:
             print(r.stdout + r.stderr)
             raise RuntimeError("link failed")
-    if not defines and lib_path is None:
-        build_dropin(objs, headers, nvcc, obj_dir, force, verbose)
+    build_dropin(objs, headers, nvcc, obj_dir, force, verbose)
     return lib_out
 
 
@@ -103,5 +99,4 @@ def build_dropin(attn_objs, headers, nvcc, obj_dir, force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
-                defines=tuple(a[2:] for a in sys.argv[1:] if a.startswith("-D"))))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

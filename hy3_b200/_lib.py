@@ -3,8 +3,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# HY3A_LIB selects another build of the same library (kernel tuning experiments)
-LIB_PATH = os.environ.get("HY3A_LIB") or os.path.join(HERE, "libhy3attn.so")
+LIB_PATH = os.path.join(HERE, "libhy3attn.so")
 
 
 class Hy3AttnError(RuntimeError):

@@ -108,7 +108,7 @@ void hy3a_destroy(hy3a_ctx *ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     cudaFree(ctx->pool); cudaFree(ctx->d_block_table); cudaFree(ctx->d_vs_max); cudaFree(ctx->d_inv_freq);
     cudaFree(ctx->d_norm_w); cudaFree(ctx->d_batch); cudaFree(ctx->d_partials); cudaFree(ctx->d_counters); cudaFree(ctx->d_err);
-    cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v); cudaFree(ctx->d_trace);
+    cudaFree(ctx->d_pf_k); cudaFree(ctx->d_pf_v);
     for (int l = 0; l < HY3A_MAX_LAYERS; l++) { cudaFree(ctx->pf_mk[l]); cudaFree(ctx->pf_mv[l]); }
     hy3a_shard_disconnect(ctx);
     cudaFree(ctx->shard_local);
@@ -198,8 +198,6 @@ int hy3a_create(const hy3a_config *cfg, hy3a_ctx **out) {
     CREATE_CUDA(cudaMalloc(&ctx->d_partials, ctx->partial_records * 8 * HY3A_REC_FLOATS * sizeof(float)));
     CREATE_CUDA(cudaMalloc(&ctx->d_counters, (size_t)2 * cfg->max_batch * cfg->kv_head_count * sizeof(unsigned)));
     CREATE_CUDA(cudaMemsetAsync(ctx->d_counters, 0, (size_t)2 * cfg->max_batch * cfg->kv_head_count * sizeof(unsigned), ctx->stream));
-    CREATE_CUDA(cudaMalloc(&ctx->d_trace, (size_t)512 * 64 * sizeof(unsigned long long)));
-    CREATE_CUDA(cudaMemsetAsync(ctx->d_trace, 0, (size_t)512 * 64 * sizeof(unsigned long long), ctx->stream));
     CREATE_CUDA(cudaMalloc(&ctx->d_err, HY3A_ERR_WORDS * sizeof(unsigned)));
     CREATE_CUDA(cudaMemsetAsync(ctx->d_err, 0, HY3A_ERR_WORDS * sizeof(unsigned), ctx->stream));
     /* operand mirrors of the chunked prefill, sized for a whole sequence, when a context that takes chunks (max_batch >= 16:

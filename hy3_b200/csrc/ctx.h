@@ -77,7 +77,6 @@ struct hy3a_ctx {
     int pf_mntok[HY3A_MAX_LAYERS];  /* tokens converted and still valid */
     int pf_mseq;                    /* the sequence all mirrors belong to, -1 = none */
     size_t pf_mbytes, pf_mbudget;   /* allocated / allowed bytes of mirrors (HY3A_PF_MIRROR_MB, 0 = no mirrors) */
-    unsigned long long *d_trace; /* [512][64] timestamps written by trace builds of the decode kernel */
     unsigned int *d_err;  /* HY3A_ERR_WORDS words: kernels record bounded-wait timeouts / bad indices here */
     size_t partial_records;
 

@@ -326,7 +326,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
     const int g = lane >> 2, tig = lane & 3;
     const int n = batch.n, G = cache.kv_heads;
     const int cta = blockIdx.x;
-    if (warp == 0) TRACE(0);
 
     int *s_prefix = reinterpret_cast<int *>(s_dyn + kFixed);
     const unsigned bar_base = smem_u32(s_dyn + kFixed + a.prefix_bytes);
@@ -458,7 +457,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
 
     if (idle && !SHARD) return;   /* sharded: idle CTAs may still own the fold of rows without local keys */
 
-    if (warp == 0) TRACE(1);
 
     if (STAGED && warp == kWarps) {
         /* ================= producer warp: one lane streams the CTA's pages into the ring */
@@ -484,7 +482,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, sg.hl) * (size_t)cache.page_bytes;
                     mbar_expect_tx(bar_base + 8 * stage, (unsigned)geom.page_bytes);
                     bulk_g2s(ring_base + stage * (unsigned)geom.page_bytes, page, (unsigned)geom.page_bytes, bar_base + 8 * stage, pol);
-                    TRACE(32 + it);
                 }
                 u = sg.seg_u0 + sg.p_end;
             }
@@ -643,7 +640,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             pscale = exp2f((float)E);
         }
 
-        if (warp == 0) TRACE(2);
         warp_state st;
         st.m = -INFINITY; st.l = 0.f;
 #pragma unroll
@@ -686,7 +682,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 if (16 * gi + 16 <= valid) granule<DT, true, true>(st, sq, qf, nullptr, spage, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
                 else if (16 * gi < valid) granule<DT, true, false>(st, sq, qf, nullptr, spage, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
                 mbar_arrive(bar_base + 64 + 8 * stage); /* every thread of the 8 warps that share a page releases it */
-                if (warp == 0) TRACE(3 + (x - it * 8u) / kWarps);
             } else {
                 if (16 * gi >= valid) continue; /* warp-uniform */
                 const int block = cache.block_table[(size_t)sg.seq * cache.max_blocks_per_seq + p];
@@ -726,7 +721,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             acc[0] += o4.x * f; acc[1] += o4.y * f; acc[2] += o4.z * f; acc[3] += o4.w * f;
         }
         consumer_sync(); /* s_o / s_ml free again */
-        if (warp == 0) TRACE(24);
 
         /* ---- how many CTAs share this segment? */
         const int c_first = aligned ? al_first : (int)(((sg.seg_u0 + 1) * C + U - 1) / U) - 1;
@@ -753,7 +747,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                  * piece while the others have left.  The remaining pieces leave at once.                          */
                 const int F = npieces >= 8 ? 8 : (npieces >= 4 ? 4 : 2), hpf = 8 / F, piece = cta - c_first;
                 if (tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.counters + sidx) : "memory");
-                TRACE(25);
                 if (piece >= F) continue;   /* CTA-uniform */
                 if (tid == 0) {
                     /* bounded wait for the other pieces (they are resident: one CTA per SM at most) */
@@ -808,7 +801,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     const unsigned old = atomicAdd(a.counters + a.n_counters + sidx, 1u);
                     if (old == (unsigned)(F - 1)) { a.counters[sidx] = 0u; a.counters[a.n_counters + sidx] = 0u; }
                 }
-                TRACE(26);
             } else {
                 /* ---- a CTA may hold pieces of several segments (large batches): the LAST CTA to arrive folds, nobody waits */
                 if (tid == 0) {
@@ -817,7 +809,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     s_flag = (old == (unsigned)(npieces - 1));
                 }
                 consumer_sync();
-                TRACE(25);
                 if (!s_flag) continue;   /* CTA-uniform */
                 /* fold all pieces with the rule of hy3_gpu.cu:233-247.  The pieces' records (contiguous) are fetched
                  * into the merge buffer with 16-byte asynchronous copies issued by all threads at once and folded
@@ -850,7 +841,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 }
                 if (tid == 0) a.counters[sidx] = 0u; /* self-reset for the next launch */
                 consumer_sync();   /* the landing zone is read; the next segment may reuse the buffer */
-                TRACE(26);
             }
         }
         const bool fin = red && h >= h_lo && h < h_hi;   /* this thread finishes its (head, 4 dims) of the segment */
@@ -870,7 +860,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     shard_store_line(rec + 1 + (d4 >> 1), acc[0], acc[1], flag);
                     shard_store_line(rec + 2 + (d4 >> 1), acc[2], acc[3], flag);
                 }
-                if (warp == 0) TRACE(27);
                 shard_fold_args fa;
                 fa.rec0 = a.gathered + ro; fa.rank_stride = (size_t)n * G * 8 * kShardLines; fa.err = a.err;
                 fa.out = a.out + (size_t)row * a.out_stride + ((size_t)(cache.kv_head_begin + hl) * 8 + h) * HY3A_D + d4;
@@ -884,7 +873,6 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 } else {
                     shard_fold<kShardBatch>(fa);
                 }
-                if (warp == 0) TRACE(30);
                 __syncwarp();                /* every lane of the head's warp has read the use count */
                 if (d4 == 0) a.shard_round[seg * 8 + h] = flag;
             }
@@ -1003,9 +991,7 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
      * GPU the folders only hold their SMs longer, which delays the next launch's CTAs there.  Its folders wait for the other
      * pieces, so every CTA of the grid must be resident */
     a.spread = ctx->shard_slot >= 0 && ctx->decode_ctas <= ctx->sm_count;
-    a.trace = ctx->d_trace;
     a.early_prefetch = ctx->use_pdl && !ctx->bulk_write_pending;
-    { static int l2p = -1; if (l2p < 0) { const char *e = getenv("HY3A_L2_PREFETCH"); l2p = e ? atoi(e) : 1; } a.l2_prefetch = l2p; }
     if (ctx->shard_slot >= 0) {   /* set by hy3a_decode_step_sharded around this call */
         const int W = ctx->shard_world, slot = ctx->shard_slot;
         const size_t n_seg = (size_t)ctx->shard_rows * ctx->cfg.kv_head_count;
@@ -1081,7 +1067,7 @@ extern "C" int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, siz
     a.scratch = reinterpret_cast<float *>(scratch);
     a.counters = reinterpret_cast<unsigned *>(scratch + kNoAllocRecordBytes);
     a.n_counters = kNoAllocRows;
-    a.err = ctx->d_err; a.layer = layer; a.trace = ctx->d_trace;
+    a.err = ctx->d_err; a.layer = layer;
     a.early_prefetch = 0;
     hy3a_cache_view cv = hy3a_view(ctx);
     hy3a_batch_view bv = hy3a_bview(ctx);
@@ -1094,14 +1080,6 @@ extern "C" int hy3a_decode_noalloc(hy3a_ctx *ctx, int layer, const float *q, siz
     ctx->launches++;
     ctx->bulk_write_pending = 0;
     if (e != cudaSuccess) return hy3a_fail(ctx, HY3A_ECUDA, "decode_noalloc launch: %s", cudaGetErrorString(e));
-    return HY3A_OK;
-}
-
-/* Development aid (trace builds): copy the per-CTA timestamps of the last decode launch to the host. */
-extern "C" int hy3a_debug_read_trace(hy3a_ctx *ctx, unsigned long long *out, int n_ctas) {
-    if (!ctx || !ctx->d_trace) return HY3A_EINVAL;
-    HY3A_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    HY3A_CUDA(ctx, cudaMemcpy(out, ctx->d_trace, (size_t)n_ctas * 64 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     return HY3A_OK;
 }
 

@@ -14,7 +14,6 @@
 
 /* Argument block of the decode kernels (filled by hy3a_launch_decode / hy3a_decode_noalloc in decode.cu). */
 struct hy3a_decode_args {
-    unsigned long long *trace; /* [gridDim.x][64] timestamps (trace builds only) */
     const float *q;
     size_t q_stride;
     float *out;
@@ -39,7 +38,6 @@ struct hy3a_decode_args {
      * the CTA that streams the page of the newest slot quantises and appends the new K / V row   */
     int fused;
     int early_prefetch;   /* pages below the newest slots may be fetched before griddepcontrol.wait */
-    int l2_prefetch;      /* ask L2 for the pages beyond the ring as soon as the preceding kernel is complete */
     const float *q_in, *k_in, *v_in;
     size_t qi_stride, ki_stride, vi_stride;
     float *q_out;         /* optional: normalised + rotated queries, fp32 [n][64][128] */
@@ -65,13 +63,6 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
-
-#ifdef HY3A_DECODE_TRACE
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(slot) do { if (lane == 0 && (slot) < 64) a.trace[(size_t)blockIdx.x * 64 + (slot)] = gtime(); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#endif
 
 typedef hy3a_decode_args decode_args;
 

@@ -40,15 +40,6 @@
 #include "ctx.h"
 #include "decode_common.cuh"
 #include "rowops.cuh"
-#ifndef HY3A_X
-#define HY3A_X 0
-#endif
-#ifdef HY3A_DECODE_TRACE
-__device__ __forceinline__ long long clk64() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) :: "memory"); return t; }
-#define CK(i) do { if (ck) ck[i] = clk64(); } while (0)
-#else
-#define CK(i) do { } while (0)
-#endif
 
 namespace {
 
@@ -132,8 +123,7 @@ __device__ __forceinline__ void sts16(unsigned addr, unsigned v) { asm volatile(
 /* One 32-token group of one score warp: S = Qd . K^T, the group's max / sum, digits of w into the P^T tile.
  * FULL: all 32 tokens are valid.  spage: shared address of the page; pt: shared address of the slot's P^T tile. */
 template <bool FULL>
-__device__ __forceinline__ void score_group(u_misc &mi, int slot, unsigned sq, float qf, unsigned spage, unsigned pt, int k_off0, int k_off1, int gi, int g, int tig, int lane, int valid, long long *ck = nullptr) {
-    CK(2);
+__device__ __forceinline__ void score_group(u_misc &mi, int slot, unsigned sq, float qf, unsigned spage, unsigned pt, int k_off0, int k_off1, int gi, int g, int tig, int lane, int valid) {
     unsigned ksw[4], vsw[4];
 #pragma unroll
     for (int nb = 0; nb < 4; nb++) {
@@ -159,16 +149,10 @@ __device__ __forceinline__ void score_group(u_misc &mi, int slot, unsigned sq, f
             for (int j = 0; j < 2; j++) {
                 const unsigned b0 = kk == 0 ? kr[j][0].x : (kk == 1 ? kr[j][0].y : (kk == 2 ? kr[j][0].z : kr[j][0].w));
                 const unsigned b1 = kk == 0 ? kr[j][1].x : (kk == 1 ? kr[j][1].y : (kk == 2 ? kr[j][1].z : kr[j][1].w));
-#if HY3A_X == 3
-                c[2 * half + j][0] += (int)(b0 ^ qa.x); c[2 * half + j][1] += (int)(b1 ^ qa.y); c[2 * half + j][2] += (int)(b0 + qa.z); c[2 * half + j][3] += (int)(b1 + qa.w);
-#else
                 imma16832(c[2 * half + j], qa, b0, b1);
-#endif
             }
         }
     }
-    asm volatile("" :: "r"(c[0][0] ^ c[1][1] ^ c[2][2] ^ c[3][3]) : "memory");
-    CK(3);
     /* logits (base 2) of head g for tokens 32 gi + 8 nb + 2 tig + e, and the V scales of those tokens */
     float s[4][2], vs[4][2];
 #pragma unroll
@@ -198,9 +182,6 @@ __device__ __forceinline__ void score_group(u_misc &mi, int slot, unsigned sq, f
         unsigned hb[2], lb[2];
 #pragma unroll
         for (int e = 0; e < 2; e++) {
-#if HY3A_X == 2
-            hb[e] = __float_as_uint(s[nb][e]); lb[e] = __float_as_uint(vs[nb][e] + inv + msafe); lsum += s[nb][e];
-#else
             const float p = ex2(s[nb][e] - msafe);               /* -inf -> 0 */
             lsum += p;
             const float d = p * vs[nb][e] * inv;                 /* 0 .. 32258 */
@@ -209,7 +190,6 @@ __device__ __forceinline__ void score_group(u_misc &mi, int slot, unsigned sq, f
             const float u = fmaf(hf, -254.f, d + magic);
             hb[e] = __float_as_uint(t);
             lb[e] = __float_as_uint(u);
-#endif
         }
         /* byte column 32 gi + 8 nb + 2 tig of rows g (high digit) and 8 + g (low digit); 16-byte chunk c of a row sits at
          * chunk c ^ (row & 7) = c ^ g */
@@ -217,17 +197,13 @@ __device__ __forceinline__ void score_group(u_misc &mi, int slot, unsigned sq, f
         sts16(pt_row + col, prmt(hb[0], hb[1], 0x0040u));
         sts16(pt_row + 1024u + col, prmt(lb[0], lb[1], 0x0040u));
     }
-    CK(4);
     lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
     lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
     if (tig == 0) { mi.meta_m[slot][gi][g] = mx; mi.meta_l[slot][gi][g] = lsum; }
     if (lane == 0) mi.meta_wb[slot][gi] = wb;
     /* the digits were written through the generic proxy; the tensor core reads through the async proxy */
-    CK(5);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    CK(6);
     mbar_arrive(UBAR(mi.pfull[slot]));
-    CK(7);
 }
 
 template <bool SHARD>
@@ -247,7 +223,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
     const unsigned ring_base = s_base + ring_off;
     const int qw = warp - kQkWarp0, qtid = tid - kQkWarp0 * 32;      /* score-warp numbering (negative for the other roles) */
     const bool is_qk = warp >= kQkWarp0;
-    if (warp == 0) TRACE(0);
 
     /* ---- prologue: everything here reads only what the host wrote.  The loads are issued together. */
     const int rl_d0 = (lane >> 4) * 64 + (lane & 15) * 4;
@@ -281,7 +256,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 0) TRACE(11);
     if (n > 1) {
         if (warp == 0) {
             int carry = 0;
@@ -368,7 +342,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
         if (warp == kIssWarp) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(mi.tmem), "n"(kSlots * 64) : "memory");
         return;
     }
-    if (warp == 0) TRACE(12);
     segment sg0;                                                    /* the CTA's first piece */
     sg0.row = 0; sg0.hl = 0;
     if (!idle) sg0 = locate(s_prefix, batch, n, G, u_begin, u_end);
@@ -403,13 +376,10 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
             asm volatile("prefetch.global.L2 [%0];" ::"l"(kp));
         }
     }
-    if (warp == kQkWarp0) TRACE(13);
-    if (warp == kIssWarp) TRACE(14);
     fence_before();
     __syncthreads();
     fence_after();
     const unsigned tmem = mi.tmem;
-    if (warp == 0) TRACE(15);
 
     /* From here on the kernel touches memory that the preceding kernel in the stream may produce (queries, the newest KV
      * slot, scratch records): wait for it -- except the producer lane, which first starts the copies of pages that lie
@@ -419,7 +389,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
-    if (warp == kQkWarp0) TRACE(1);
     /* rows with no keys on this rank: zero output / empty partial (hy3_gpu.cu:197-199) */
     if (is_qk)
         for (int i = cta; i < n; i += gridDim.x) {
@@ -478,9 +447,8 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                     if (p + 1 < sg.p_end) block_next = bt[p + 1];   /* in flight while we wait for the stage */
                     /* before the preceding kernel is known to be complete only pages that lie wholly below the newest
                      * slot may be fetched, and only into stages that were never used */
-                    if (it == (unsigned)kStages && a.l2_prefetch == 2) prefetch_rest();   /* L2 is coherent: no need to know the preceding kernel complete */
                     if (!waited && (it >= (unsigned)kStages || (p + 1) * HY3A_PT > sg.len - 2)) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
-                    if (it == (unsigned)kStages && a.l2_prefetch == 1) {
+                    if (it == (unsigned)kStages) {
                         /* the ring is full and nothing is consumed yet: once the score warps hold their queries (their loads are
                          * not to queue behind this burst), ask L2 for the rest */
                         UWAIT(mi.qload, 0u, 4u);
@@ -505,7 +473,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                     }
                     mbar_expect_tx(UBAR(mi.rfull[stage]), (unsigned)geom.page_bytes);
                     bulk_g2s(ring_base + stage * (unsigned)kStageBytes, page, (unsigned)geom.page_bytes, UBAR(mi.rfull[stage]), pol);
-                    TRACE(32 + it);
                 }
                 u = sg.seg_u0 + sg.p_end;
             }
@@ -622,7 +589,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                 const float4 rv = *reinterpret_cast<const float4 *>(&mi.rr[slot][hq0]);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 acc[0] *= rv.x; acc[1] *= rv.y; acc[2] *= rv.z; acc[3] *= rv.w;
-#if HY3A_X != 1
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     const float4 fv = *reinterpret_cast<const float4 *>(&mi.fa[slot][8 * q + hq0]);
@@ -631,13 +597,9 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                     acc[2] = fmaf((float)(c[q][2] * 254 + c[q][6]), fv.z, acc[2]);
                     acc[3] = fmaf((float)(c[q][3] * 254 + c[q][7]), fv.w, acc[3]);
                 }
-#else
-                acc[0] += __int_as_float(c[0][0] ^ c[1][1] ^ c[2][2] ^ c[3][3] ^ c[0][4] ^ c[1][5] ^ c[2][6] ^ c[3][7]);
-#endif
                 fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(UBAR(mi.sfree[slot]));          /* TMEM slot, P^T tile, meta and factors of the slot are free */
-                if (warp == 0 && it < 8u) TRACE(48 + it);
             }
             /* hand the finished piece to the epilogue (score warps) */
             float *s_acc = reinterpret_cast<float *>(s_dyn + kOffAcc);
@@ -703,7 +665,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
             }
             qk_sync();
             const float qf = mi.qf[g];
-            if (qw == 0) TRACE(2);
 
             /* group X = 4 * (ring position of the page) + group-in-page; warp w takes X = w (mod kQkWarps) */
             const unsigned it_end = it + (unsigned)(sg.p_end - sg.p_begin);
@@ -714,30 +675,16 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                 const unsigned stage = pit % (unsigned)kStages, rph = (pit / (unsigned)kStages) & 1u;
                 const unsigned slot = pit % (unsigned)kSlots, sph = (pit / (unsigned)kSlots) & 1u;
                 const unsigned spage = ring_base + stage * (unsigned)kStageBytes;
-#ifdef HY3A_DECODE_TRACE
-                long long ckv[8];
-                long long *ck = (qw == 0 && lane == 0 && (X - it * 4u) / kQkWarps == 2u) ? ckv : nullptr;   /* the third call of score warp 0 */
-                CK(0);
-#else
-                long long *ck = nullptr;
-#endif
                 UWAIT(mi.rfull[stage], rph, 2u);
-                CK(1);
                 UWAIT(mi.sfree[slot], sph ^ 1u, 3u);        /* the accumulators are through with the page that used this slot before */
                 const unsigned pt = s_base + kOffPt + slot * 2048u;
-                if (32 * gi + 32 <= valid) score_group<true>(mi, (int)slot, sq, qf, spage, pt, k_off0, k_off1, gi, g, tig, lane, valid, ck);
-                else score_group<false>(mi, (int)slot, sq, qf, spage, pt, k_off0, k_off1, gi, g, tig, lane, valid, ck);
-#ifdef HY3A_DECODE_TRACE
-                if (ck) { for (int i = 1; i < 8; i++) a.trace[(size_t)blockIdx.x * 64 + 63 - 8 + i] = (unsigned long long)(ckv[i] - ckv[i - 1]); }
-#endif
-                if (qw == 0) TRACE(3 + (X - it * 4u) / kQkWarps);
+                if (32 * gi + 32 <= valid) score_group<true>(mi, (int)slot, sq, qf, spage, pt, k_off0, k_off1, gi, g, tig, lane, valid);
+                else score_group<false>(mi, (int)slot, sq, qf, spage, pt, k_off0, k_off1, gi, g, tig, lane, valid);
             }
             it = it_end;
 
             /* ---- the piece of this CTA, from the accumulators: thread -> (head, 4 dims) */
-            if (qw == 0) TRACE(19);
             epi_sync();
-            if (qw == 0) TRACE(20);
             const bool red = qtid < 256;
             const int h = (qtid >> 5) & 7, d4 = (qtid & 31) * 4;
             float M = mi.ml[h][0], L = mi.ml[h][1], acc[4];
@@ -746,7 +693,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                 acc[0] = o4.x; acc[1] = o4.y; acc[2] = o4.z; acc[3] = o4.w;
             }
             qk_sync();   /* everybody holds its share: the accumulators may overwrite the hand-over area (next piece) */
-            if (qw == 0) TRACE(21);
 
             /* ---- how many CTAs share this segment? */
             const int c_first = aligned ? al_first : (int)(((sg.seg_u0 + 1) * C + U - 1) / U) - 1;
@@ -763,7 +709,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                     rec[2 + d4] = acc[0]; rec[3 + d4] = acc[1]; rec[4 + d4] = acc[2]; rec[5 + d4] = acc[3];
                 }
                 qk_sync();   /* the record is complete in CTA scope; the release below publishes it */
-                if (qw == 0) TRACE(24);
                 if (aligned && a.spread) {
                     /* CTA-aligned segments: the fold is spread over the first F pieces (see decode.cu) */
                     const int F = npieces >= 8 ? 8 : (npieces >= 4 ? 4 : 2), hpf = 8 / F, piece = cta - c_first;
@@ -828,7 +773,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                         mi.flag = (old == (unsigned)(npieces - 1));
                     }
                     qk_sync();
-                    if (qw == 0) TRACE(25);
                     if (!mi.flag) continue;   /* CTA-uniform */
                     /* fold all pieces with the rule of hy3_gpu.cu:233-247: the records are fetched with 16-byte asynchronous
                      * copies issued by all threads at once into the page ring when it is idle (CTA-aligned segments: this
@@ -898,7 +842,6 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                 qk_sync();
                 continue;
             }
-            if (qw == 0) TRACE(26);
             if (!fin) continue;
             if (a.user_partials) {
                 float *rec = a.user_partials + ((size_t)row * G * 8 + (size_t)hl * 8 + h) * HY3A_PARTIAL_FLOATS;
@@ -939,12 +882,9 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                 for (unsigned ph = 0; ph < 2; ph++)
                     for (unsigned spin = 0; spin < (1u << 14) && !mbar_test(UBAR(mi.rfull[st]), ph); spin++) __nanosleep(64);
         }
-        if (warp == kQkWarp0) TRACE(27);
         fence_before();
         __syncthreads();
-        if (warp == kQkWarp0) TRACE(28);
         if (warp == kIssWarp) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kSlots * 64) : "memory");
-        if (warp == kIssWarp) TRACE(29);
     }
 }
 

@@ -65,13 +65,22 @@ static hy3_weight dense_f32(hy3h_arena *a, uint64_t rows, uint64_t cols, float s
     for (uint64_t i = 0; i < rows * cols; i++) p[i] = mean + s * pool_at(a, off, i);
     return make_weight(a, p, 0, rows, cols);
 }
-static uint16_t f2h(float f) {   /* round-to-nearest-even float -> half, normal range only */
+#define HY3H_MIN_NORMAL_HALF 6.2e-5f
+static uint16_t f2h(float f) {   /* round-to-nearest-even float -> half (subnormal halves included) */
     uint32_t x; memcpy(&x, &f, 4);
     const uint32_t sign = (x >> 16) & 0x8000u;
     int e = (int)((x >> 23) & 0xFF) - 127 + 15;
     uint32_t m = x & 0x7FFFFFu;
-    if (e <= 0) return (uint16_t)sign;
     if (e >= 31) return (uint16_t)(sign | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)sign;
+        m |= 0x800000u;                          /* the implicit one becomes explicit: value = m * 2^(e - 1 - 23 - 14) halves' ulps */
+        const int shift = 14 - e;                /* 14 .. 24 */
+        uint32_t h = m >> shift;
+        const uint32_t rem = m & ((1u << shift) - 1u), half = 1u << (shift - 1);
+        if (rem > half || (rem == half && (h & 1u))) h++;
+        return (uint16_t)(sign | h);
+    }
     uint32_t h = (uint32_t)(e << 10) | (m >> 13);
     const uint32_t rem = m & 0x1FFFu;
     if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) h++;
@@ -81,14 +90,21 @@ static hy3_weight dense_f16(hy3h_arena *a, uint64_t rows, uint64_t cols, float s
     uint16_t *p = arena_alloc(a, rows * cols * sizeof(uint16_t));
     const float s = scale / sqrtf((float)cols);
     const uint64_t off = h_next(&a->rng) % HY3H_POOL;
-    for (uint64_t i = 0; i < rows * cols; i++) p[i] = f2h(s * pool_at(a, off, i));
+    for (uint64_t i = 0; i < rows * cols; i++) {
+        /* kept in the normal half range: the engine's own half decoder (hy3.c:354-369) reads zero and subnormal halves as
+         * (1 + mantissa / 1024) * 2^-15, the device reads them as IEEE does -- such values would only compare the decoders */
+        float v = s * pool_at(a, off, i);
+        if (fabsf(v) < HY3H_MIN_NORMAL_HALF) v = copysignf(HY3H_MIN_NORMAL_HALF, v);
+        p[i] = f2h(v);
+    }
     return make_weight(a, p, 1, rows, cols);
 }
 /* Q4_K tensor of random blocks whose values have mean ~0 and rms ~ scale / sqrt(cols) */
 static hy3_weight dense_q4k(hy3h_arena *a, uint64_t rows, uint64_t cols, float scale) {
     const uint64_t nb = rows * cols / 256;
     uint8_t *p = arena_alloc(a, nb * 144);
-    const float d = scale / sqrtf((float)cols) / 143.f;      /* code * sc has rms ~ 143 around its mean */
+    float d = scale / sqrtf((float)cols) / 143.f;            /* code * sc has rms ~ 143 around its mean */
+    if (d < HY3H_MIN_NORMAL_HALF / 0.75f) d = HY3H_MIN_NORMAL_HALF / 0.75f;   /* d and dmin stay normal halves (see dense_f16) */
     for (uint64_t b = 0; b < nb; b++) {
         uint8_t *blk = p + b * 144;
         const uint16_t hd = f2h(d * (0.75f + 0.5f * (float)(h_next(&a->rng) & 0xFF) / 255.f)), hm = f2h(d * 7.5f);

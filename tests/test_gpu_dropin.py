@@ -7,8 +7,13 @@ set of MoE tensors.  The same token sequence goes through hy3_eval on the CPU (h
 hy3_eval_gpu, with the call pattern of hy3_generate (hy3.c:1487-1573): a prompt in one call (chunked prefill for all
 but its last token, HY3_PREFILL_CHUNK), cache_len set back to a shorter prefix (hy3.c:1514), then single-token calls.
 
-Bound: the CPU path keeps fp32 K/V; the backend stores FP16 / INT8 K/V and computes attention in fp16, through 80
-layers.  The logits must agree within the relative RMS stated per cache type below (measured: see the printed line).
+Bound: the CPU path keeps fp32 K/V; the backend stores FP16 / INT8 / INT4 K/V and computes attention in fp16, through 80
+layers.  The logits must agree within the relative RMS stated per cache type below (measured on B200 with this model:
+fp16 5e-5 .. 8e-5, int8 2.3e-2 .. 3.0e-2, int4 7e-2 .. 9.2e-2; the printed line shows the values of the run).
+
+The test tensors hold no zero or subnormal half: the engine's CPU half decoder (hy3.c:354-369) reads those as
+(1 + mantissa / 1024) * 2^-15 while the device decodes IEEE halves, so such values would compare the two decoders, not
+the backends.
 """
 import ctypes as C
 import os
@@ -19,7 +24,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 VOCAB = 1024
-OUT_SCALE = 0.15      # every layer perturbs the residual stream a little: rounding differences are not amplified chaotically
+OUT_SCALE = 0.05      # every layer perturbs the residual stream a little: rounding differences are not amplified chaotically
 
 
 class Tokens(C.Structure):
@@ -95,7 +100,7 @@ def model_and_reference(engine):
     host.hy3h_model_free(m)
 
 
-@pytest.mark.parametrize("kv,bound", [("fp16", 2e-2), ("int8", 6e-2), ("int4", 4e-1)])
+@pytest.mark.parametrize("kv,bound", [("fp16", 1e-3), ("int8", 6e-2), ("int4", 2e-1)])
 def test_eval_gpu_matches_cpu_eval(engine, model_and_reference, monkeypatch, capfd, kv, bound):
     host, gpu = engine
     m, ref = model_and_reference
@@ -157,7 +162,7 @@ def test_q4k_and_f16_tensors(engine, monkeypatch):
     """Routed experts kept as Q4_K blocks on the device and an F16 query projection: against the engine's own
     dequantising CPU matmul (hy3.c:1007-1041, :1080-1155)."""
     host, gpu = engine
-    m = host.hy3h_model_new(7, VOCAB, 2, 12, 1, OUT_SCALE)
+    m = host.hy3h_model_new(7, VOCAB, 2, 12, 1, 0.4)     # Q4_K scales must be normal halves: the expert down projection cannot be made smaller
     assert m
     host.hy3h_set_expert_used(m, 2)
     for k in ("HY3_KV_INT4", "HY3_PREFILL_CHUNK"):
