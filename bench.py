@@ -746,6 +746,12 @@ def run_ours(args):
 
 
 def main():
+    # the contract is ONE JSON line on stdout: libraries that write to file descriptor 1 themselves (NCCL prints its version
+    # there) go to stderr; the JSON line goes to the real stdout
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    sys.stdout = real_stdout
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
