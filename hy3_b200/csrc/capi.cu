@@ -76,7 +76,21 @@ int hy3a_decode_schedule(int n, const int *kv_lens, int kv_heads, int n_ctas, in
     const long long U = P * kv_heads;
     if (total_units) *total_units = U;
     long long b = U, e = U;
-    if (U > 0 && (long long)n * kv_heads < n_ctas) {
+    bool aligned = U > 0 && (long long)n * kv_heads < n_ctas;
+    if (aligned && (long long)n * kv_heads * 4 > n_ctas) {
+        /* the aligned split is kept only while its rounding leaves no CTA more than 5/4 of the even share */
+        const long long spare = (long long)n_ctas - (long long)rows_ne * kv_heads, PG = P * kv_heads;
+        long long worst = 0;
+        for (int r = 0; r < n; r++) {
+            long long p = kv_lens[r] > 0 ? (kv_lens[r] + HY3A_PAGE_TOKENS - 1) / HY3A_PAGE_TOKENS : 0;
+            if (p == 0) continue;
+            long long c = 1 + spare * p / PG;
+            if (c > p) c = p;
+            if ((p + c - 1) / c > worst) worst = (p + c - 1) / c;
+        }
+        aligned = worst * 4 <= (PG + n_ctas - 1) / n_ctas * 5 + 4;
+    }
+    if (aligned) {
         const long long spare = (long long)n_ctas - (long long)rows_ne * kv_heads;
         long long base = 0, pre = 0;
         for (int r = 0; r < n; r++) {

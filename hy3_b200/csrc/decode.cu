@@ -51,6 +51,7 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kFixedO = kWarps * 8 * HY3A_D * 4;
 constexpr int kFixedML = ((kWarps * 8 * 2 * 4) + 127) / 128 * 128;
 constexpr int kFixedQ = 8 * 32 * 16;
+constexpr int kBarBytes = 256;      /* mbarriers of the page ring: empty[8], full[16] */
 constexpr int kFixed = kFixedO + kFixedML + kFixedQ;   /* bytes of shared memory in front of the page-count prefix */
 constexpr bool kPSplit = true;                         /* carry the fp16 residual of P in MMA rows 8-15 */
 constexpr int kRecFloats = HY3A_REC_FLOATS;             /* floats per head record in the merge scratch (130 used) */
@@ -329,7 +330,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
 
     int *s_prefix = reinterpret_cast<int *>(s_dyn + kFixed);
     const unsigned bar_base = smem_u32(s_dyn + kFixed + a.prefix_bytes);
-    const unsigned ring_base = bar_base + 128;
+    const unsigned ring_base = bar_base + kBarBytes;
 
     /* ---- schedule: prefix of pages per row */
     for (int i = tid; i < n; i += blockDim.x) {
@@ -340,7 +341,8 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
         s_prefix[0] = 0;
         s_abort = 0;
         if (STAGED) {
-            for (int i = 0; i < a.stages; i++) { mbar_init(bar_base + 8 * i, 1); mbar_init(bar_base + 64 + 8 * i, 256); }
+            for (int i = 0; i < a.stages; i++) mbar_init(bar_base + 8 * i, 256);          /* empty[stage]: every thread of the 8 warps that share a page */
+            for (int i = 0; i < 2 * a.stages; i++) mbar_init(bar_base + 64 + 8 * i, 1);   /* full[page mod 2 stages]: the producer's expect_tx */
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
     }
@@ -369,7 +371,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
      *    query set-up and the fold twice and becomes the critical path of a small batch);
      *  - many segments: one contiguous, equally sized range per CTA over all units.
      * In both, never more CTAs than units, and the CTAs sharing a segment are contiguous.       */
-    const bool aligned = (long long)n * G < (long long)gridDim.x;
+    const bool aligned = (long long)n * G < (long long)gridDim.x && aligned_split_balanced(s_prefix, n, G, gridDim.x, lane);
     int C = (long long)gridDim.x < U ? (int)gridDim.x : (int)U;
     long long u_begin = 0, u_end = 0;
     int al_first = 0, al_pieces = 1;
@@ -477,11 +479,12 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     /* before the preceding kernel is known to be complete only pages that lie wholly below
                      * the newest slot may be fetched, and only into stages that were never used            */
                     if (!waited && (it >= (unsigned)a.stages || (p + 1) * HY3A_PT > sg.len - 2)) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
-                    ok = mbar_wait(bar_base + 64 + 8 * stage, phase ^ 1u, &s_abort, a.err, 1u);
+                    ok = mbar_wait(bar_base + 8 * stage, phase ^ 1u, &s_abort, a.err, 1u);
                     if (!ok) break;
                     const uint8_t *page = cache.pool + hy3a_page_index(cache, block, a.layer, sg.hl) * (size_t)cache.page_bytes;
-                    mbar_expect_tx(bar_base + 8 * stage, (unsigned)geom.page_bytes);
-                    bulk_g2s(ring_base + stage * (unsigned)geom.page_bytes, page, (unsigned)geom.page_bytes, bar_base + 8 * stage, pol);
+                    const unsigned full = bar_base + 64 + 8 * (it % (2u * (unsigned)a.stages));
+                    mbar_expect_tx(full, (unsigned)geom.page_bytes);
+                    bulk_g2s(ring_base + stage * (unsigned)geom.page_bytes, page, (unsigned)geom.page_bytes, full, pol);
                 }
                 u = sg.seg_u0 + sg.p_end;
             }
@@ -490,8 +493,8 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 /* gave up: let the copies already issued land before the CTA's shared memory goes away */
                 const unsigned first = it > (unsigned)a.stages ? it - (unsigned)a.stages : 0u;
                 for (unsigned j = first; j < it; j++) {
-                    const unsigned stage = j % (unsigned)a.stages, phase = (j / (unsigned)a.stages) & 1u;
-                    for (unsigned spin = 0; spin < (1u << 20) && !mbar_test(bar_base + 8 * stage, phase); spin++) __nanosleep(64);
+                    const unsigned fb = j % (2u * (unsigned)a.stages), fphase = (j / (2u * (unsigned)a.stages)) & 1u;
+                    for (unsigned spin = 0; spin < (1u << 20) && !mbar_test(bar_base + 64 + 8 * fb, fphase); spin++) __nanosleep(64);
                 }
             }
         }
@@ -654,9 +657,15 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
             const int gi = (int)(x & 7u), p = sg.p_begin + (int)(pit - it);
             const int valid = min(HY3A_PT, sg.len - p * HY3A_PT);
             if (STAGED) {
-                const unsigned stage = pit % (unsigned)a.stages, phase = (pit / (unsigned)a.stages) & 1u;
+                const unsigned q2 = pit / (2u * (unsigned)a.stages), r2 = pit - q2 * 2u * (unsigned)a.stages;   /* ring round pair, position in it */
+                const unsigned stage = r2 < (unsigned)a.stages ? r2 : r2 - (unsigned)a.stages;
                 const unsigned spage = ring_base + stage * (unsigned)geom.page_bytes;
-                mbar_wait(bar_base + 8 * stage, phase, &s_abort, a.err, 2u);
+                /* the page's "full" barrier is one of 2 x stages: a warp holds granules in 8 of every 11 pages, so it may skip a
+                 * use of a stage, and an mbarrier wait only knows the parity of a phase.  With one barrier per stage the warp's next
+                 * wait on that stage could pass on the stale phase while the skipped page is still landing (seen with the two-stage
+                 * ring of FP16 pages).  With two barriers per stage the phase a warp can miss is two ring rounds old: every page the
+                 * warp has consumed since was filled after that one had been filled, consumed and its stage filled again. */
+                mbar_wait(bar_base + 64 + 8 * r2, q2 & 1u, &s_abort, a.err, 2u);
                 if (a.fused && a.k_in && p == ((sg.len - 1) >> 7) && gi == (((sg.len - 1) & 127) >> 4)) {
                     /* fused append: this warp holds the only granule that contains the newest slot.  It
                      * normalises, rotates and quantises the new K row and quantises the new V row exactly
@@ -665,7 +674,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     const int d0 = (lane >> 4) * 64 + (lane & 15) * 4, tok = (sg.len - 1) & 127;
                     const int block = cache.block_table[(size_t)sg.seq * cache.max_blocks_per_seq + p];
                     uint8_t *gp = cache.pool + hy3a_page_index(cache, block, a.layer, hl) * (size_t)cache.page_bytes;
-                    uint8_t *sp = s_dyn + kFixed + a.prefix_bytes + 128 + (size_t)stage * geom.page_bytes;
+                    uint8_t *sp = s_dyn + kFixed + a.prefix_bytes + kBarBytes + (size_t)stage * geom.page_bytes;
                     const int kvh = cache.kv_head_begin + hl;
                     float4 kv4 = *reinterpret_cast<const float4 *>(a.k_in + (size_t)row * a.ki_stride + (size_t)kvh * HY3A_D + d0);
                     float y[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
@@ -681,7 +690,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 }
                 if (16 * gi + 16 <= valid) granule<DT, true, true>(st, sq, qf, nullptr, spage, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
                 else if (16 * gi < valid) granule<DT, true, false>(st, sq, qf, nullptr, spage, geom, k_off, v_off, sc_off, gi, tig, valid, pscale);
-                mbar_arrive(bar_base + 64 + 8 * stage); /* every thread of the 8 warps that share a page releases it */
+                mbar_arrive(bar_base + 8 * stage); /* every thread of the 8 warps that share a page releases it */
             } else {
                 if (16 * gi >= valid) continue; /* warp-uniform */
                 const int block = cache.block_table[(size_t)sg.seq * cache.max_blocks_per_seq + p];
@@ -782,7 +791,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                     }
                     asm volatile("cp.async.wait_all;" ::: "memory");
                     __syncwarp();
-                    const float *zf = reinterpret_cast<const float *>(s_dyn + kFixed + a.prefix_bytes + 128 + zone);
+                    const float *zf = reinterpret_cast<const float *>(s_dyn + kFixed + a.prefix_bytes + kBarBytes + zone);
                     for (int c = 0; c < npieces; c++) {
                         const float *pr = zf + (size_t)c * kRecFloats;
                         const float pm = pr[0], pl = pr[1];
@@ -868,7 +877,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 if (STAGED && aligned && (size_t)a.stages * geom.page_bytes >= (size_t)8 * 8 * kShardLines * 16) {
                     /* CTA-aligned segments: the page ring is idle by now and holds all 8 ranks' records at once, so
                      * every rank is polled in the same round */
-                    fa.stage = reinterpret_cast<const uint4 *>(s_dyn + kFixed + a.prefix_bytes + 128);
+                    fa.stage = reinterpret_cast<const uint4 *>(s_dyn + kFixed + a.prefix_bytes + kBarBytes);
                     shard_fold<8>(fa);
                 } else {
                     shard_fold<kShardBatch>(fa);
@@ -942,7 +951,7 @@ static cudaError_t launch_decode_dt(hy3a_ctx *ctx, const hy3a_cache_view &cv, co
     a.prefix_bytes = (int)prefix;
     if (ctx->decode_stages >= 2) {
         a.stages = ctx->decode_stages;
-        const size_t smem = kFixed + prefix + 128 + (size_t)a.stages * ctx->geom.page_bytes;
+        const size_t smem = kFixed + prefix + kBarBytes + (size_t)a.stages * ctx->geom.page_bytes;
         const bool shard = a.n_dest > 0;
         if (!attr_set[DT][shard ? 2 : 1]) {
             cudaError_t e = shard ? cudaFuncSetAttribute(hy3a_decode_kernel<DT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax)
@@ -965,7 +974,7 @@ static cudaError_t launch_decode_dt(hy3a_ctx *ctx, const hy3a_cache_view &cv, co
             if (e != cudaSuccess) return e;
             attr_set[DT][0] = true;
         }
-        hy3a_decode_kernel<DT, false><<<grid, kThreads, kFixed + prefix + 128, ctx->stream>>>(cv, bv, a);
+        hy3a_decode_kernel<DT, false><<<grid, kThreads, kFixed + prefix + kBarBytes, ctx->stream>>>(cv, bv, a);
     }
     return cudaGetLastError();
 }
@@ -973,7 +982,7 @@ static cudaError_t launch_decode_dt(hy3a_ctx *ctx, const hy3a_cache_view &cv, co
 /* Pages that fit in the ring for a given page size and batch capacity. */
 int hy3a_decode_ring_capacity(int page_bytes, int max_batch) {
     const size_t prefix = ((size_t)(max_batch + 1) * sizeof(int) + 127) & ~(size_t)127;
-    long room = (long)kSmemMax - (long)kFixed - (long)prefix - 128;
+    long room = (long)kSmemMax - (long)kFixed - (long)prefix - kBarBytes;
     int s = room > 0 ? (int)(room / page_bytes) : 0;
     return s > 8 ? 8 : s;
 }

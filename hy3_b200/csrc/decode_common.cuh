@@ -94,6 +94,33 @@ __device__ __forceinline__ segment locate(const int *s_prefix, const hy3a_batch_
     return sg;
 }
 
+/* The CTA-aligned split gives every (row, KV head) segment whole CTAs in proportion to its pages.  With few segments that is
+ * balanced to a page; when the segments are about as many as the CTAs the rounding leaves some CTAs with far more pages than
+ * the even share (64 rows of one KV head on 148 CTAs: up to 1.75 x), and the plain equal split over all units is the better
+ * one.  Returns whether the aligned split stays within 5/4 of the even share.  Every lane takes rows lane, lane + 32, ...;
+ * call with all lanes of the warp; the result is the same in every warp. */
+__device__ __forceinline__ bool aligned_split_balanced(const int *s_prefix, int n, int G, unsigned grid, int lane) {
+    if ((unsigned)(n * G) * 4u <= grid) return true;   /* at least four CTAs per segment */
+    const unsigned long long P = (unsigned)s_prefix[n];
+    int ne = 0;
+    for (int r = lane; r < n; r += 32) ne += (s_prefix[r + 1] != s_prefix[r]);
+    ne = __reduce_add_sync(0xffffffffu, ne);
+    const unsigned long long spare = grid - (unsigned)(ne * G), PG = P * (unsigned)G;
+    if (PG == 0) return true;
+    unsigned worst = 0;
+    for (int r = lane; r < n; r += 32) {
+        const unsigned p = (unsigned)(s_prefix[r + 1] - s_prefix[r]);
+        if (p == 0) continue;
+        unsigned long long c = 1ull + spare * p / PG;
+        if (c > p) c = p;
+        const unsigned w = (unsigned)((p + c - 1ull) / c);
+        worst = worst > w ? worst : w;
+    }
+    worst = __reduce_max_sync(0xffffffffu, worst);
+    const unsigned long long even = (PG + grid - 1ull) / grid;
+    return (unsigned long long)worst * 4ull <= even * 5ull + 4ull;
+}
+
 /* ---- shared-memory / mbarrier / bulk-copy primitives ---------------------------------- */
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint4 lds16(unsigned addr) {

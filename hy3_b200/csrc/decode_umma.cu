@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
     const unsigned Pn = (unsigned)s_prefix[n];
     const long long U = (long long)G * Pn;
     bool idle = (U == 0);
-    const bool aligned = (long long)n * G < (long long)gridDim.x;
+    const bool aligned = (long long)n * G < (long long)gridDim.x && aligned_split_balanced(s_prefix, n, G, gridDim.x, lane);
     const int C = (long long)gridDim.x < U ? (int)gridDim.x : (int)U;
     long long u_begin = 0, u_end = 0;
     int al_first = 0, al_pieces = 1;

@@ -70,6 +70,31 @@ def test_decode_long_context_many_ctas(cuda, oracle, dt, variant):
     ctx.close()
 
 
+@pytest.mark.parametrize("dt", ["fp16", "int4", "int8"])
+def test_decode_is_bitwise_repeatable(cuda, dt):
+    """The same launch repeated back to back gives the same bits: fold orders are fixed, and no warp may read a ring stage
+    that is still being filled (FP16 pages leave room for a two-stage ring only; a consumer warp that holds no granule of
+    a page used to be able to pass its next wait on a stale barrier phase there)."""
+    import torch
+    from hy3_b200 import Hy3Attn
+    n = 40000
+    ctx = Hy3Attn(kv_dtype=dt, n_layers=2, max_batch=2, max_tokens=n + 128)
+    for l in range(2):
+        ctx.fill_random(l, 0, 0, n, 3 + l)
+    q = torch.randn((1, 64, 128), device=cuda, generator=torch.Generator(device=cuda).manual_seed(5))
+    ctx.batch_set([0], [n - 1])
+    ref = [ctx.decode(l, q).clone() for l in range(2)]
+    torch.cuda.synchronize()
+    differing = 0
+    for _ in range(60):
+        outs = [(l, ctx.decode(l, q)) for _ in range(3) for l in range(2)]
+        torch.cuda.synchronize()
+        differing += sum(0 if torch.equal(o, ref[l]) else 1 for l, o in outs)
+    ctx.sync()
+    ctx.close()
+    assert differing == 0, "%d of 360 launches differ from the first" % differing
+
+
 def test_decode_ragged_batch_and_poison(cuda, oracle):
     """Several sequences of different lengths in one launch; cache bytes past each length are poison."""
     import torch
