@@ -1,5 +1,6 @@
 /*
- * decode.cu -- split-KV GQA decode attention over the paged FP16 / INT8 / INT4 cache.
+ * decode.cu -- split-KV GQA decode attention over the paged FP16 and INT4 caches (INT8 caches: decode_umma.cu),
+ * the launch entry points of all three, and the merge kernel.
  *
  * Replaces attention_split_kv[_int4]_kernel + attention_reduce_kernel of the reference
  * (hy3_gpu.cu:183-247, :274-325).  The reference runs one warp per (query head, split),
@@ -10,13 +11,13 @@
  *   S[16 x 8]   = Q2[16 x 128] . K^T    rows 0-7 = the 8 heads, rows 8-15 = a residual of the
  *                                       same 8 queries (M=16 is the MMA minimum, so the second
  *                                       half of the tile buys near-fp32 queries for free).
- *                                       INT8/INT4 caches: integer MMA (m16n8k32.s8) directly on
- *                                       the stored codes -- Q is split into two int8 digits
+ *                                       INT4 cache: integer MMA (m16n8k32.s8) directly on the
+ *                                       stored nibbles -- Q is split into two int8 digits
  *                                       (q ~ sq*(hi + lo/254)), the products are exact, and no
  *                                       per-element conversion of K is needed at all.
  *                                       FP16 cache: m16n8k16.f16 with Q = fp16 + fp16 residual.
- *   O[16 x 128] += P[16 x 16] . V       m16n8k16.f16; INT8/INT4 codes become fp16 exactly with one
- *                                       byte-permute (or lop3) + one fp16 subtract per pair.
+ *   O[16 x 128] += P[16 x 16] . V       m16n8k16.f16; INT4 codes become fp16 exactly with one lop3 +
+ *                                       one fp16 subtract (or fma) per pair.
  *
  * The per-token scales are applied once per score (K) and once per probability (V), never
  * per element.  The contraction dimension of Q.K^T and the output dimension of P.V are
@@ -32,8 +33,8 @@
  * several CTAs each writes an {m, l, acc} record and the LAST CTA to arrive (atomic
  * counter) folds them -- the LSE-merge epilogue, no second launch.
  *
- * Roofline: HBM.  Algorithmic bytes per (token, KV head): 512 (FP16), 260 (INT8),
- * 132 (INT4); per token and layer x8.
+ * Roofline: HBM.  Algorithmic bytes per (token, KV head): 512 (FP16), 132 (INT4); per token and
+ * layer x8.
  */
 #include <cuda_fp16.h>
 #include <math.h>
@@ -96,11 +97,7 @@ __device__ __forceinline__ void mma16816(float c[4], const unsigned a[4], unsign
 }
 
 /* ---- exact integer-code -> fp16x2 conversions of V --------------------------------------
- * V codes are stored offset-binary (INT8: c+128, INT4: n+8; see append.cu), so that no sign
- * fix-up is needed here.  INT8: placing a byte under the exponent byte 0x64 gives the fp16
- * number 1024 + (c+128); subtracting 1152 leaves c exactly.  sel picks which two bytes
- * become the (low, high) halves.                                                          */
-__device__ __forceinline__ unsigned cvt_u8(unsigned x, unsigned sel) { return hsub2(prmt(x, 0x64646464u, sel), 0x64806480u); }
+ * INT4 V codes are stored offset-binary (n+8; see append.cu), so that no sign fix-up is needed here. */
 /* INT4: nibbles (i, i+4) become one fp16x2.  Low positions: (x & 0x000f000f) | 0x6400 =
  * 1024 + (n+8), minus 1032.  High positions: (x & 0x00f000f0) | 0x6400 = 1024 + 16(n+8);
  * times 1/16 minus 72 = n.                                                               */
@@ -144,8 +141,9 @@ template <int DT, bool SM, bool FULL>
 __device__ __forceinline__ void granule(warp_state &st, unsigned sq, float qf, const uint8_t *gpage, unsigned spage, const hy3a_geom &geom,
                                         const int (&k_off)[2][4], const int (&v_off)[8], const int (&sc_off)[2], int gi, int tig, int valid,
                                         float pscale) {
-    constexpr int NK = DT == 0 ? 4 : (DT == 1 ? 2 : 1);
-    constexpr int NV = DT == 0 ? 8 : (DT == 1 ? 4 : 2);
+    static_assert(DT == 0 || DT == 2, "INT8 caches are served by decode_umma.cu");
+    constexpr int NK = DT == 0 ? 4 : 1;
+    constexpr int NV = DT == 0 ? 8 : 2;
     /* page-relative byte offsets of granule gi (16 tokens = 16 K rows = 8 V pair-rows) */
     const int gk = gi * 16 * geom.k_row, gv = geom.v_off + gi * (DT == 0 ? 16 : 8) * geom.v_prow, gs = gi * 32;
     uint4 kr[2][NK];
@@ -196,16 +194,9 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, float qf, c
         for (int kk = 0; kk < 4; kk++) {
 #pragma unroll
             for (int nb = 0; nb < 2; nb++) {
-                unsigned b0, b1;
-                if (DT == 1) {
-                    b0 = kk == 0 ? kr[nb][0].x : (kk == 1 ? kr[nb][0].y : (kk == 2 ? kr[nb][0].z : kr[nb][0].w));
-                    b1 = kk == 0 ? kr[nb][NK - 1].x : (kk == 1 ? kr[nb][NK - 1].y : (kk == 2 ? kr[nb][NK - 1].z : kr[nb][NK - 1].w));
-                } else {
-                    /* two's-complement nibbles: moving a nibble to the top of its byte gives 16 x code as int8 */
-                    const unsigned w = kk == 0 ? kr[nb][0].x : (kk == 1 ? kr[nb][0].y : (kk == 2 ? kr[nb][0].z : kr[nb][0].w));
-                    b0 = (w << 4) & 0xF0F0F0F0u;
-                    b1 = w & 0xF0F0F0F0u;
-                }
+                /* two's-complement nibbles: moving a nibble to the top of its byte gives 16 x code as int8 */
+                const unsigned w = kk == 0 ? kr[nb][0].x : (kk == 1 ? kr[nb][0].y : (kk == 2 ? kr[nb][0].z : kr[nb][0].w));
+                const unsigned b0 = (w << 4) & 0xF0F0F0F0u, b1 = w & 0xF0F0F0F0u;
                 imma16832((kk & 1) ? co[nb] : ce[nb], qa[kk], b0, b1);
             }
         }
@@ -266,18 +257,7 @@ __device__ __forceinline__ void granule(warp_state &st, unsigned sq, float qf, c
         }
     }
     /* ---- O += P.V over 16 n-blocks of 8 output dims */
-    if (DT == 1) {
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-            unsigned a4[4] = {vr[half].x, vr[half].y, vr[half].z, vr[half].w};
-            unsigned b4[4] = {vr[2 + half].x, vr[2 + half].y, vr[2 + half].z, vr[2 + half].w};
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                mma16816(st.o[8 * half + 2 * k], pa, cvt_u8(a4[k], 0x4240u), cvt_u8(b4[k], 0x4240u));
-                mma16816(st.o[8 * half + 2 * k + 1], pa, cvt_u8(a4[k], 0x4341u), cvt_u8(b4[k], 0x4341u));
-            }
-        }
-    } else if (DT == 2) {
+    if (DT == 2) {
         unsigned a4[4] = {vr[0].x, vr[0].y, vr[0].z, vr[0].w};
         unsigned b4[4] = {vr[1].x, vr[1].y, vr[1].z, vr[1].w};
 #pragma unroll
@@ -508,18 +488,13 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
 #pragma unroll
     for (int nb = 0; nb < 2; nb++) {
         int tok = 8 * nb + g;
-        if (DT == 1) { k_off[nb][0] = hy3a_k_chunk_off<1>(tok, tig); k_off[nb][1] = hy3a_k_chunk_off<1>(tok, tig + 4); k_off[nb][2] = k_off[nb][3] = 0; }
-        else if (DT == 2) { k_off[nb][0] = hy3a_k_chunk_off<2>(tok, tig); k_off[nb][1] = k_off[nb][2] = k_off[nb][3] = 0; }
+        if (DT == 2) { k_off[nb][0] = hy3a_k_chunk_off<2>(tok, tig); k_off[nb][1] = k_off[nb][2] = k_off[nb][3] = 0; }
         else { for (int i = 0; i < 4; i++) k_off[nb][i] = hy3a_k_chunk_off<0>(tok, tig + 4 * i); }
         sc_off[nb] = 2 * (8 * nb + 2 * tig);
     }
     {
         int pr0 = tig, pr1 = pr0 + 4;
-        if (DT == 1) {
-            v_off[0] = hy3a_v_chunk_off<1>(pr0, g); v_off[1] = hy3a_v_chunk_off<1>(pr0, g + 8);
-            v_off[2] = hy3a_v_chunk_off<1>(pr1, g); v_off[3] = hy3a_v_chunk_off<1>(pr1, g + 8);
-            v_off[4] = v_off[5] = v_off[6] = v_off[7] = 0;
-        } else if (DT == 2) {
+        if (DT == 2) {
             v_off[0] = hy3a_v_chunk_off<2>(pr0, g); v_off[1] = hy3a_v_chunk_off<2>(pr1, g);
             for (int i = 2; i < 8; i++) v_off[i] = 0;
         } else {
@@ -592,7 +567,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                 float m = fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w)));
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                vb = (unsigned)__half_as_ushort(__float2half(__fadd_rn(__fdiv_rn(m, DT == 1 ? 127.f : 7.f), 1e-8f)));
+                vb = (unsigned)__half_as_ushort(__float2half(__fadd_rn(__fdiv_rn(m, 7.f), 1e-8f)));
             }
             if (lane == 0) s_vnew = vb;
         }
