@@ -241,38 +241,44 @@ def timed_decode_steps(torch, dev, ctx, lens, steps, warm, enqueue, sync_all=Non
 
 
 def batch_section(torch, dev, kind, ntok=262144):
-    """Secondary decode workloads on one GPU, one layer each, device-timed back-to-back fused steps:
+    """Secondary decode workloads on one GPU, device-timed fused steps:
     'ragged'  -- configs[4]: 64 sequences, lengths 1024 + (rng % 64513) (seeded), INT8 KV, one token per sequence per
-                 step (all 8 KV heads on this GPU);
-    'long'    -- configs[3]: batch 1, INT4 KV, `ntok` positions, YaRN factor 4 (attn_factor on q and k)."""
+                 step (all 8 KV heads on this GPU), one layer per step (4.2 GB per launch);
+    'long'    -- configs[3]: batch 1, INT4 KV, `ntok` positions, YaRN factor 4 (attn_factor on q and k); a step is the
+                 token's pass over 4 layer caches, launched back to back as a model's layers are."""
     from hy3_b200 import Hy3Attn
     if kind == "ragged":
-        kv, lens = "int8", ragged_lengths()
+        kv, lens, layers = "int8", ragged_lengths(), 1
         what = "configs[4]: 64 sequences, lengths uniform in [1024, 65536] (seeded), INT8 KV, 1 layer, all 8 KV heads on one GPU"
     else:
-        kv, lens = "int4", [ntok]
-        what = "configs[3]: batch 1, INT4 KV, %d positions, YaRN factor 4, 1 layer, unsharded" % ntok
+        kv, lens, layers = "int4", [ntok], 4
+        what = "configs[3]: batch 1, INT4 KV, %d positions, YaRN factor 4, 4 layer caches per step, unsharded" % ntok
     B = len(lens)
     steps, warm = 20, 4
-    ctx = Hy3Attn(kv_dtype=kv, n_layers=1, max_seqs=B, max_batch=B, max_tokens=sum(lens) + (steps + warm + 129) * B,
+    ctx = Hy3Attn(kv_dtype=kv, n_layers=layers, max_seqs=B, max_batch=B, max_tokens=sum(lens) + (steps + warm + 129) * B,
                   max_tokens_per_seq=max(lens) + steps + warm + 129, device=dev.index)
     if kind == "long":
         ctx.set_rope(*yarn4_table())
-    for i, n in enumerate(lens):
-        ctx.fill_random(0, i, 0, n, SEED + i)
+    for l in range(layers):
+        for i, n in enumerate(lens):
+            ctx.fill_random(l, i, 0, n, SEED + i + 1000 * l)
     q = torch.randn((B, H, D), device=dev)
     k = torch.randn((B, G, D), device=dev)
     v = torch.randn((B, G, D), device=dev)
-    out = torch.zeros((B, H, D), device=dev)
-    times = timed_decode_steps(torch, dev, ctx, lens, steps, warm, lambda: ctx.decode_step(0, q, k, v, out=out))
+    out = torch.zeros((layers, B, H, D), device=dev)
+
+    def step():
+        for l in range(layers):
+            ctx.decode_step(l, q, k, v, out=out[l])
+    times = [t / layers for t in timed_decode_steps(torch, dev, ctx, lens, steps, warm, step)]
     ctx.sync()
     ctx.close()
     ms = statistics.median(times)
     nbytes = (sum(lens) + B * (warm + steps // 2)) * BYTES_PER_TOKEN[kv]
     gbs = nbytes / ms / 1e6
     return {"metric": METRIC, "value": gbs, "unit": UNIT, "workload": what, "ms_per_launch": ms, "ms_per_launch_min": min(times),
-            "ms_per_launch_max": max(times), "algorithmic_bytes_per_launch": nbytes,
-            "l2": "%.2f GB streamed per launch, far beyond L2" % (nbytes / 1e9), "roofline": hbm_roofline(KERNEL_NAME[kv], gbs)}
+            "ms_per_launch_max": max(times), "launches_per_step": layers, "algorithmic_bytes_per_launch": nbytes,
+            "l2": "%.2f GB streamed per step, far beyond L2" % (layers * nbytes / 1e9), "roofline": hbm_roofline(KERNEL_NAME[kv], gbs)}
 
 
 def prefill_section(torch, dev, kv="fp16", prompt=8192, chunk=512, prefix=0):
@@ -358,26 +364,28 @@ def gather_max(torch, dist, dev, x):
 
 
 def long_sharded_section(torch, dist, dev, rank, world, total):
-    """configs[3]: ONE sequence of `total` positions, INT4 KV, YaRN factor 4, one layer, split by token range
-    (hy3_b200.sharding.sequence_range); the in-kernel exchange over peer memory folds the ranks' records.  Strong
-    scaling: the same total on rank 0 alone is timed right after, in the same process."""
+    """configs[3]: ONE sequence of `total` positions, INT4 KV, YaRN factor 4, split by token range
+    (hy3_b200.sharding.sequence_range); a step is the token's pass over 4 layer caches; the in-kernel exchange over peer
+    memory folds the ranks' records.  Strong scaling: the same total on rank 0 alone is timed right after, in the same
+    process."""
     from hy3_b200 import Hy3Attn
     from hy3_b200.sharding import sequence_range
-    steps, warm = 20, 4
+    steps, warm, layers = 20, 4, 4
     t0, t1 = sequence_range(rank, world, total)
     mine = t1 - t0
     owner = rank == world - 1
-    ctx = Hy3Attn(kv_dtype="int4", n_layers=1, max_batch=1, max_tokens=mine + steps + warm + 256, device=dev.index)
+    ctx = Hy3Attn(kv_dtype="int4", n_layers=layers, max_batch=1, max_tokens=mine + steps + warm + 256, device=dev.index)
     ctx.set_rope(*yarn4_table())
-    ctx.fill_random(0, 0, 0, mine, SEED + 77 * rank)
+    for l in range(layers):
+        ctx.fill_random(l, 0, 0, mine, SEED + 77 * rank + 1000 * l)
     handles = [None] * world
-    dist.all_gather_object(handles, ctx.shard_init(rank, world, 1, 1))
+    dist.all_gather_object(handles, ctx.shard_init(rank, world, layers, 1))
     ctx.shard_connect(handles)
     dist.barrier()
     q = torch.randn((1, H, D), device=dev)
     k = torch.randn((1, G, D), device=dev)
     v = torch.randn((1, G, D), device=dev)
-    out = torch.zeros((1, H, D), device=dev)
+    out = torch.zeros((layers, 1, H, D), device=dev)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     times = []
     for i in range(warm + steps):
@@ -385,10 +393,11 @@ def long_sharded_section(torch, dist, dev, rank, world, total):
         dist.barrier()
         torch.cuda.synchronize()
         ev[0].record(torch.cuda.current_stream(dev))
-        ctx.decode_step_sharded(0, 0, q, k if owner else None, v if owner else None, out=out)
+        for l in range(layers):
+            ctx.decode_step_sharded(l, l, q, k if owner else None, v if owner else None, out=out[l])
         ev[1].record(torch.cuda.current_stream(dev))
         ev[1].synchronize()
-        ms = gather_max(torch, dist, dev, ev[0].elapsed_time(ev[1]))
+        ms = gather_max(torch, dist, dev, ev[0].elapsed_time(ev[1])) / layers
         if i >= warm:
             times.append(ms)
     ctx.sync()
@@ -398,7 +407,7 @@ def long_sharded_section(torch, dist, dev, rank, world, total):
     ms = statistics.median(times)
     nbytes = (total + warm + steps // 2) * BYTES_PER_TOKEN["int4"]
     res = {"positions": total, "ms_per_launch": ms, "ms_per_launch_min": min(times), "ms_per_launch_max": max(times),
-           "value": nbytes / ms / 1e6, "unit": UNIT, "algorithmic_bytes_per_launch": nbytes}
+           "launches_per_step": layers, "value": nbytes / ms / 1e6, "unit": UNIT, "algorithmic_bytes_per_launch": nbytes}
     # the same total on one GPU (rank 0), for the strong-scaling ratio
     one = None
     if rank == 0:
@@ -698,7 +707,7 @@ def run_ours(args):
                 extra["ragged_kv_head_sharded"] = ragged_head_sharded_section(torch, dist, dev, rank, world)
             extra["long_context_int4_sharded"] = {
                 "metric": METRIC, "unit": UNIT, "scaling": "strong",
-                "workload": "configs[3]: batch 1, INT4 KV, YaRN factor 4, 1 layer, ONE sequence split by token range over %d GPUs, in-kernel LSE-merge exchange over NVLink peer memory" % world,
+                "workload": "configs[3]: batch 1, INT4 KV, YaRN factor 4, 4 layer caches per step, ONE sequence split by token range over %d GPUs, in-kernel LSE-merge exchange over NVLink peer memory" % world,
                 "contexts": [long_sharded_section(torch, dist, dev, rank, world, t) for t in (262144, 1048576)]}
     clocks = sampler.stop() if rank == 0 else None
 
