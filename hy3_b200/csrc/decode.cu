@@ -729,7 +729,7 @@ __global__ void __launch_bounds__(kThreads + (STAGED ? 32 : 0), 1) hy3a_decode_k
                  * (one warp per head: 33 16-byte asynchronous copies per record and lane 0 one more, all records in
                  * flight at once, landing in the idle page ring), instead of one CTA pulling every head of every
                  * piece while the others have left.  The remaining pieces leave at once.                          */
-                const int F = npieces >= 8 ? 8 : (npieces >= 4 ? 4 : 2), hpf = 8 / F, piece = cta - c_first;
+                const int Fmax = a.spread, F = npieces >= Fmax ? Fmax : (npieces >= 4 && Fmax >= 4 ? 4 : (npieces >= 2 && Fmax >= 2 ? 2 : 1)), hpf = 8 / F, piece = cta - c_first;
                 if (tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.counters + sidx) : "memory");
                 if (piece >= F) continue;   /* CTA-uniform */
                 if (tid == 0) {
@@ -974,7 +974,7 @@ int hy3a_launch_decode(hy3a_ctx *ctx, int layer, const float *q, size_t q_stride
     /* the spread fold pays off where the epilogue is the cross-GPU exchange (8 CTAs store to the peers instead of one); on one
      * GPU the folders only hold their SMs longer, which delays the next launch's CTAs there.  Its folders wait for the other
      * pieces, so every CTA of the grid must be resident */
-    a.spread = ctx->shard_slot >= 0 && ctx->decode_ctas <= ctx->sm_count;
+    a.spread = (ctx->shard_slot >= 0 && ctx->decode_ctas <= ctx->sm_count) ? 4 : 0;   /* folders per segment: 4 measured best on 8 GPUs (8: 28.8, 4: 27.8, 2: 27.8, 1: 29.2 us per layer) */
     a.early_prefetch = ctx->use_pdl && !ctx->bulk_write_pending;
     if (ctx->shard_slot >= 0) {   /* set by hy3a_decode_step_sharded around this call */
         const int W = ctx->shard_world, slot = ctx->shard_slot;

@@ -31,7 +31,7 @@ struct hy3a_decode_args {
     float *scratch;       /* merge records: [(gridDim.x + n*kv_heads)][8][HY3A_REC_FLOATS] */
     unsigned int *counters; /* [2][n_counters]: arrivals per (row, KV head) segment, then finished folds */
     int n_counters;
-    int spread;           /* CTA-aligned segments may spread their fold over several CTAs (the whole grid is resident) */
+    int spread;           /* > 0: CTA-aligned segments spread their fold over up to this many of their CTAs (the whole grid is resident) */
     unsigned int *err;
     int layer;
     /* fused step (fused != 0): the kernel itself normalises + rotates the queries read from q_in and

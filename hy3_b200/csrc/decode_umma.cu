@@ -711,7 +711,7 @@ __global__ void __launch_bounds__(kUThreads, 1) hy3a_decode_umma_kernel(hy3a_cac
                 qk_sync();   /* the record is complete in CTA scope; the release below publishes it */
                 if (aligned && a.spread) {
                     /* CTA-aligned segments: the fold is spread over the first F pieces (see decode.cu) */
-                    const int F = npieces >= 8 ? 8 : (npieces >= 4 ? 4 : 2), hpf = 8 / F, piece = cta - c_first;
+                    const int Fmax = a.spread, F = npieces >= Fmax ? Fmax : (npieces >= 4 && Fmax >= 4 ? 4 : (npieces >= 2 && Fmax >= 2 ? 2 : 1)), hpf = 8 / F, piece = cta - c_first;
                     if (qtid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.counters + sidx) : "memory");
                     if (piece >= F) continue;   /* CTA-uniform */
                     if (qtid == 0) {
