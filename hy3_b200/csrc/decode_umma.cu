@@ -14,18 +14,23 @@
  *                                        8 heads x {high, low} int8 digit of w = p * vscale(token) / wb, wb = the largest
  *                                        V scale of the 32 tokens; products and sums are exact integers
  *
- * Roles (18 warps):
- *   warps 0-7   accumulators: thread = (head dim, 4 of the 8 heads).  Per page they read the four groups' integer results
- *               from TMEM and add them, scaled, to 4 fp32 registers.
- *   warp 8      page producer: bulk copies (cp.async.bulk + mbarrier transaction counts) into a ring of pages.
- *   warp 9      MMA issuer + bookkeeper: when the four groups' digits of a page are in shared memory one lane issues the four
- *               tcgen05.mma and one tcgen05.commit; then the warp (lane = (group, head)) does the online-softmax
- *               bookkeeping of the page -- running max, rescale factor, denominator, the factor of every (group, head) --
- *               once for all accumulators, while the tensor core works.
- *   warps 10-17 score warps: a warp takes a 32-token group: 16 integer MMAs, scales, the group's own max (2 shuffles),
+ * Roles (19 warps, coupled by mbarriers only):
+ *   warps 0-7   accumulators: thread = (head dim = TMEM lane, 4 of the 8 heads).  Per page they read the four groups' integer
+ *               results from TMEM (tcgen05.ld) and add them, scaled, to 4 fp32 registers.  Before the stream starts they
+ *               also run the fused append (one warp per new row).
+ *   warp 8      page producer (one lane): bulk copies (cp.async.bulk + mbarrier transaction counts, evict-first in L2) into a
+ *               ring of pages; the first ring fill runs before the preceding kernel is known to be complete (pages below
+ *               the newest slot are immutable), and once the queries are loaded it asks L2 for the pages beyond the ring.
+ *   warp 9      MMA issuer (one lane): when the four groups' digits of a page are in shared memory it issues the four
+ *               tcgen05.mma back to back, one tcgen05.commit for the accumulators and one that frees the ring stage.  It
+ *               does nothing else: scalar code between two MMAs of a lane costs more than the MMA.
+ *   warp 10     bookkeeper (lane = (group, head)): the online-softmax bookkeeping of the page -- running max, rescale factor,
+ *               denominator, the factor of every (group, head) -- once for all accumulators, while the tensor core works.
+ *   warps 11-18 score warps: a warp takes a 32-token group: 16 integer MMAs, scales, the group's own max (2 shuffles),
  *               8 exponentials per lane, digits, 8 two-byte stores into the P^T tile, {max, sum, wb} for the bookkeeper.
  *               No output accumulators, no conversion of V: about 250 instructions per 32 tokens instead of 860.
- *               The same warps run the query set-up, the fused append and the epilogue (records, merge, exchange).
+ *               The same warps run the query set-up and the epilogue (records, merge, exchange).
+ *   Every waiter of an mbarrier waits for every phase of it, in order (a wait only knows a phase's parity).
  *
  * Every wait is bounded; a wait that runs out raises a CTA-wide abort flag and records a code in the context's error
  * word, every later wait returns at once, all roles keep their control flow to the end and TMEM is released.
