@@ -298,6 +298,44 @@ def test_kv_head_shard_writes_only_its_heads(cuda, oracle):
     ctx.close()
 
 
+@pytest.mark.parametrize("dt", ["int8", "int4"])
+def test_one_kv_head_of_a_ragged_batch(cuda, oracle, dt):
+    """A context that owns ONE KV head of 60 sequences (the KV-head shard of a ragged batch on 8 GPUs): fewer segments than
+    CTAs, but so many that giving every segment whole CTAs would leave some CTAs with far more pages than others -- the
+    kernel then takes the equal split over all units (CTAs straddle segments).  A fused step, checked per sequence."""
+    import torch
+    from hy3_b200 import Hy3Attn
+    from hy3_b200.attn import decode_schedule
+    rng = np.random.default_rng(11)
+    lens0 = [int(x) for x in rng.integers(100, 6000, size=60)]
+    B = len(lens0)
+    # the host mirror of the schedule says: not the aligned split (ranges are equal to a page)
+    sizes = [u1 - u0 for u0, u1 in (decode_schedule([n + 1 for n in lens0], 1, 148, c)[1:] for c in range(148))]
+    assert max(sizes) - min(sizes) <= 1
+    hb = 5
+    ctx = Hy3Attn(kv_dtype=dt, n_layers=1, kv_head_begin=hb, kv_head_count=1, max_seqs=B, max_batch=B,
+                  max_tokens=sum(lens0) + 256 * B, max_tokens_per_seq=8192)
+    for s_, n0 in enumerate(lens0):
+        ctx.fill_random(0, s_, 0, n0, 900 + s_)
+    q = oracle.fill_normal((B, 64, 128), SEED, 431)
+    k = oracle.fill_normal((B, 8, 128), SEED, 432)
+    v = oracle.fill_normal((B, 8, 128), SEED, 433)
+    tq, tk, tv = (torch.from_numpy(x).to(cuda) for x in (q, k, v))
+    qo = torch.zeros((B, 64, 128), dtype=torch.float32, device=cuda)
+    out = torch.full((B, 64, 128), 7.0, dtype=torch.float32, device=cuda)
+    ctx.batch_set(list(range(B)), lens0)
+    ctx.decode_step(0, tq, tk, tv, out=out, q_out=qo)
+    ctx.sync()
+    out, qo = out.cpu().numpy(), qo.cpu().numpy()
+    assert (out[:, :8 * hb] == 7.0).all() and (out[:, 8 * hb + 8:] == 7.0).all()          # only the owned heads are written
+    for s_ in range(0, B, 7):
+        ks, vs = ctx.export_kv(0, s_, 0, lens0[s_] + 1)
+        Kf, Vf = slots_to_float(oracle, ks, dt), slots_to_float(oracle, vs, dt)
+        want = oracle.attention(qo[s_], Kf, Vf)
+        check_attention(out[s_][8 * hb:8 * hb + 8], want[8 * hb:8 * hb + 8], "seq %d len %d" % (s_, lens0[s_] + 1))
+    ctx.close()
+
+
 def test_errors_are_codes_not_exits(cuda, oracle):
     import torch
     from hy3_b200 import Hy3Attn, Hy3AttnError
