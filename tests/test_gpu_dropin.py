@@ -180,3 +180,29 @@ def test_q4k_and_f16_tensors(engine, monkeypatch):
     finally:
         gpu.hy3_gpu_free(m)
         host.hy3h_model_free(m)
+
+
+def test_cache_capacity_is_an_error_code(engine, model_and_reference, monkeypatch):
+    """A call that would run past the KV pool (HY3_KV_TOKENS) returns -1 with a message (the reference grows by realloc + copy,
+    hy3_gpu.cu:692-698, and exits when that fails); the context stays usable for a sequence that fits."""
+    host, gpu = engine
+    m, ref = model_and_reference
+    for k in ("HY3_KV_INT4", "HY3_KV_FP16"):
+        monkeypatch.delenv(k, raising=False)
+    monkeypatch.setenv("HY3_PREFILL_CHUNK", "64")
+    monkeypatch.setenv("HY3_KV_TOKENS", "128")
+    assert gpu.hy3_gpu_init(m, 0) == 0
+    try:
+        host.hy3h_set_cache_len(m, 0)
+        toks = [(7 * i + 3) % VOCAB for i in range(200)]
+        arr = (C.c_int * len(toks))(*toks)
+        t = Tokens(arr, len(toks), len(toks))
+        logits = np.zeros(VOCAB, np.float32)
+        pos = C.c_int(-1)
+        assert gpu.hy3_eval_gpu(m, C.byref(t), logits.ctypes.data_as(C.POINTER(C.c_float)), C.byref(pos)) == -1
+        assert b"HY3_KV_TOKENS" in gpu.hy3_gpu_last_error(m)
+        host.hy3h_set_cache_len(m, 0)
+        got, _ = eval_gpu(gpu, m, PROMPT)                    # chunk 64 > 8 tokens: one chunk + the last token
+        assert rel_rms(got, ref[0][0]) <= 6e-2               # INT8 cache: the bound of the parity test above
+    finally:
+        gpu.hy3_gpu_free(m)
