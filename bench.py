@@ -20,8 +20,8 @@ records into every rank's gather buffer over NVLink peer memory, waits for the o
 runs the NCCL variant on three layers and the line carries the comparison ("parity").
 
 Secondary objects in the same JSON line:
-  N=1: "prefill" / "prefill_int8" / "prefill_multiturn" (configs[2], tensor roofline), "ragged_batch" (configs[4] on one
-       GPU), "long_context_int4" and "long_context_int4_1m" (configs[3] on one GPU), "reference_gpu_kernel" (the
+  N=1: "prefill" / "prefill_int8" / "prefill_multiturn" (configs[2], tensor roofline), "decode_fp16" (the headline
+       workload with an FP16 cache, 16 layer caches), "ragged_batch" (configs[4] on one GPU), "long_context_int4" and "long_context_int4_1m" (configs[3] on one GPU), "reference_gpu_kernel" (the
        reference's own CUDA decode kernels on the same GPU, context only);
   N>1: "long_context_int4_sharded" (configs[3]: ONE sequence of 262144 and of 1048576 positions split by token range,
        strong scaling, with rank 0's unsharded time of the same total beside it) and "ragged_kv_head_sharded"
@@ -279,6 +279,59 @@ def batch_section(torch, dev, kind, ntok=262144):
     return {"metric": METRIC, "value": gbs, "unit": UNIT, "workload": what, "ms_per_launch": ms, "ms_per_launch_min": min(times),
             "ms_per_launch_max": max(times), "launches_per_step": layers, "algorithmic_bytes_per_launch": nbytes,
             "l2": "%.2f GB streamed per step, far beyond L2" % (layers * nbytes / 1e9), "roofline": hbm_roofline(KERNEL_NAME[kv], gbs)}
+
+
+def decode_cache_type_section(torch, dev, kv, layers=16, ntok=NTOK):
+    """The headline workload with another cache type (FP16 KV): batch 1, `layers` independent layer caches x `ntok`
+    positions, a step = one fused launch per layer, replayed as one CUDA graph; blocks of 20 steps, median."""
+    from hy3_b200 import Hy3Attn
+    steps, warm, blocks = 20, 3, 5
+    ctx = Hy3Attn(kv_dtype=kv, n_layers=layers, max_batch=1, max_tokens=ntok + steps + 300, device=dev.index)
+    stream = torch.cuda.Stream(device=dev)
+    ctx.set_stream(stream)
+    for l in range(layers):
+        ctx.fill_random(l, 0, 0, ntok, SEED + l)
+    with torch.cuda.stream(stream):
+        q = torch.randn((layers, 1, H, D), device=dev)
+        k = torch.randn((layers, 1, G, D), device=dev)
+        v = torch.randn((layers, 1, G, D), device=dev)
+        out = torch.zeros((layers, 1, H, D), device=dev)
+
+    def step():
+        for l in range(layers):
+            ctx.decode_step(l, q[l], k[l], v[l], out=out[l])
+    ctx.batch_set([0], [ntok])
+    with torch.cuda.stream(stream):
+        step()
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    ctx.batch_set([0], [ntok + 1])
+    with torch.cuda.graph(graph, stream=stream):
+        step()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    per_launch = []
+    for b in range(blocks + 1):
+        e0.record(stream)
+        for s in range(steps if b else warm):
+            ctx.batch_set([0], [ntok + 2 + s])
+            with torch.cuda.stream(stream):
+                graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        if b:
+            per_launch.append(e0.elapsed_time(e1) / (steps * layers))
+    ctx.sync()
+    del graph
+    ctx.close()
+    ms = statistics.median(per_launch)
+    nbytes = (ntok + 2 + steps // 2) * BYTES_PER_TOKEN[kv]
+    gbs = nbytes / ms / 1e6
+    return {"metric": METRIC, "value": gbs, "unit": UNIT,
+            "workload": "%s-KV decode attention, batch 1, %d independent layer caches x %d positions, one fused launch per layer, graph of %d launches" % (kv, layers, ntok, layers),
+            "us_per_launch": ms * 1e3, "us_per_launch_min": min(per_launch) * 1e3, "us_per_launch_max": max(per_launch) * 1e3,
+            "algorithmic_bytes_per_launch": nbytes, "l2": "%.2f GB streamed per step, far beyond L2" % (layers * nbytes / 1e9),
+            "roofline": hbm_roofline(KERNEL_NAME[kv], gbs)}
 
 
 def prefill_section(torch, dev, kv="fp16", prompt=8192, chunk=512, prefix=0):
@@ -736,6 +789,7 @@ def run_ours(args):
             extra["prefill"] = prefill_section(torch, dev)
             extra["prefill_int8"] = prefill_section(torch, dev, kv="int8")
             extra["prefill_multiturn"] = prefill_section(torch, dev, prompt=1024, prefix=4096)
+            extra["decode_fp16"] = decode_cache_type_section(torch, dev, "fp16")
             extra["ragged_batch"] = batch_section(torch, dev, "ragged")
             extra["long_context_int4"] = batch_section(torch, dev, "long")
             extra["long_context_int4_1m"] = batch_section(torch, dev, "long", ntok=1048576)
