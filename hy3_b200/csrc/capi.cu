@@ -68,7 +68,8 @@ size_t hy3a_block_bytes(const hy3a_config *cfg) {
 
 int hy3a_decode_schedule(int n, const int *kv_lens, int kv_heads, int n_ctas, int cta, long long *total_units, long long *u0,
                          long long *u1) {
-    /* the same arithmetic as the head of hy3a_decode_kernel */
+    /* the same arithmetic as the head of hy3a_decode_kernel (the INT8 kernel moves a few pages between the pieces of the last
+     * segment of a single-row grid on top of it: decode_umma.cu) */
     if (n < 0 || kv_heads < 1 || n_ctas < 1 || cta < 0 || cta >= n_ctas) return HY3A_EINVAL;
     long long P = 0;
     int rows_ne = 0;
